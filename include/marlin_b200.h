@@ -1,0 +1,177 @@
+/*
+ * marlin_b200.h - C ABI of the B200 (sm_100a) Marlin weight-only GEMM / fused-MoE library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*, a
+ * cudaStream_t).  Nothing here allocates device memory unless stated; work is enqueued on the given
+ * stream and the call returns without synchronising.  Return value: 0 on success, a negative
+ * MARLIN_B200_E* code otherwise; marlin_b200_last_error() then returns a message for the calling
+ * thread.  The library is stateless apart from per-device caches (SM count, TMA descriptors keyed
+ * by weight pointer) and is safe to call from several host threads.
+ *
+ * Each declaration names the interface of the reference project (zhinianqin/marlin_v100) that it
+ * stands in for, as file:line inside that project.
+ */
+#ifndef MARLIN_B200_H_
+#define MARLIN_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MARLIN_B200_OK 0
+#define MARLIN_B200_EINVAL (-1)   /* argument check failed (the reference raises through TORCH_CHECK) */
+#define MARLIN_B200_ECUDA (-2)    /* a CUDA runtime / driver call failed */
+#define MARLIN_B200_ESCRATCH (-3) /* scratch buffer too small */
+
+/* Activation / output / scale element type. */
+#define MARLIN_B200_F16 0
+#define MARLIN_B200_BF16 1
+
+/* Weight formats.  The integer is what marlin_b200_format_from_type_id() returns for the
+ * reference's 58-bit ScalarType id (csrc/core/scalar_type.hpp:124-157, vllm/scalar_type.py:26-43)
+ * together with the scale element kind (float4_e2m1f is nvfp4 with e4m3 scales, mxfp4 with e8m0). */
+#define MARLIN_B200_FMT_U4B8 0
+#define MARLIN_B200_FMT_U4 1
+#define MARLIN_B200_FMT_U8B128 2
+#define MARLIN_B200_FMT_U8 3
+#define MARLIN_B200_FMT_FP8 4
+#define MARLIN_B200_FMT_NVFP4 5
+#define MARLIN_B200_FMT_MXFP4 6
+
+/* Scale element kinds for marlin_b200_format_from_type_id(). */
+#define MARLIN_B200_SCALE_ACT 0  /* same 16-bit type as the activations */
+#define MARLIN_B200_SCALE_E4M3 1 /* nvfp4 block scales */
+#define MARLIN_B200_SCALE_E8M0 2 /* mxfp4 block scales */
+
+/* Message of the last failed call on this host thread (never NULL). */
+const char* marlin_b200_last_error(void);
+
+/* Library version, "major.minor". */
+const char* marlin_b200_version(void);
+
+/* Maps (b_type_id, scale kind) to a MARLIN_B200_FMT_* value, or -1.
+ * Stands in for the b_type routing of csrc/quantization/marlin/marlin.cu:142-183,385-505. */
+int marlin_b200_format_from_type_id(int64_t b_type_id, int scale_kind);
+
+/* ----------------------------------------------------------------------------------------------
+ * Weight repack.  Stand in for
+ *   gptq_marlin_repack  csrc/quantization/marlin/gptq_marlin_repack.cu:399-469
+ *   awq_marlin_repack   csrc/quantization/marlin/awq_marlin_repack.cu:319-381
+ * in : GPTQ int32 [size_k / pf, size_n] (packed along K) or AWQ int32 [size_k, size_n / pf]
+ *      (packed along N with the AWQ nibble interleave), pf = 32 / num_bits, num_bits in {4, 8};
+ *      perm: int32 [size_k] source row for each destination row (act-order) or NULL.
+ * out: int32 [size_k / 16, size_n * 16 / pf], bit-identical to the reference's packed layout.
+ * Requires size_k % 16 == 0 and size_n % 64 == 0.
+ * -------------------------------------------------------------------------------------------- */
+int marlin_b200_gptq_repack(const int32_t* b_q_weight, const int32_t* perm, int32_t* out,
+                            int64_t size_k, int64_t size_n, int num_bits, void* stream);
+int marlin_b200_awq_repack(const int32_t* b_q_weight, int32_t* out, int64_t size_k, int64_t size_n,
+                           int num_bits, void* stream);
+
+/* ----------------------------------------------------------------------------------------------
+ * Dense GEMM  C[M,N] = A[M,K] * dequant(B)[K,N] (+ bias).  Stands in for
+ *   marlin_gemm  csrc/quantization/marlin/marlin.cu:83-506
+ * a           : f16/bf16 [size_m, size_k], row stride a_stride elements (multiple of 8), 16-byte
+ *               aligned.
+ * c           : same type, [size_m, size_n], contiguous.
+ * b_q_weight  : int32 [size_k / 16, size_n * 16 / pf] as produced by the repack entry points.
+ * b_scales    : [num_groups, size_n]; element type = activation type for the integer formats and
+ *               fp8, one byte for nvfp4 (special S0E5M3 bytes) and mxfp4 (e8m0), exactly as the
+ *               reference's Python wrappers prepare them.  group size = size_k / num_groups
+ *               (num_groups == 1: per-channel).
+ * b_zeros     : NULL, or [num_groups, size_n] of the activation type holding zero_point * scale
+ *               (u4 / u8 only: w = q * s - zeros).
+ * b_bias      : NULL, or [size_n] of the activation type in the reference's permuted order.
+ * global_scale: NULL, or fp32 [1] (nvfp4 only).
+ * scratch     : device buffer of at least marlin_b200_gemm_scratch_bytes() bytes (may be NULL when
+ *               that is 0).  Contents on entry are irrelevant; it is overwritten.
+ * Requires size_k % 32 == 0 and size_n % 64 == 0.  size_m == 0 is a no-op.
+ * -------------------------------------------------------------------------------------------- */
+int64_t marlin_b200_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k, int format);
+
+int marlin_b200_gemm(const void* a, void* c, const int32_t* b_q_weight, const void* b_scales,
+                     const void* b_zeros, const void* b_bias, const float* global_scale,
+                     int act_dtype, int format, int64_t size_m, int64_t size_n, int64_t size_k,
+                     int64_t a_stride, int64_t num_groups, void* scratch, int64_t scratch_bytes,
+                     void* stream);
+
+/* ----------------------------------------------------------------------------------------------
+ * Grouped expert GEMM.  Stands in for
+ *   moe_wna16_marlin_gemm  csrc/moe/marlin_moe_wna16/ops.cu:102-529
+ * Row r of block b is sid = sorted_token_ids[b * moe_block_size + r]; it is valid when
+ * 0 <= sid < size_m * top_k.  It reads A row sid / top_k, uses the weights of expert
+ * expert_ids[b] (a block with a negative id, or at or beyond num_tokens_past_padded[0], is skipped)
+ * and writes C row sid:
+ *   value = acc * global_scale[e]; value += bias[e][n] * (mul_topk_weights ? global_scale[e] : 1)
+ *   value *= mul_topk_weights ? topk_weights[sid] : 1
+ * (csrc/moe/marlin_moe_wna16/sm70_marlin_gemm.cuh:3472-3509).
+ * a [size_m, size_k] contiguous; c [size_m * top_k, size_n]; b_q_weight [E, size_k/16, size_n*16/pf];
+ * b_scales [E, num_groups, size_n]; b_zeros / b_bias / global_scale per expert ([E,G,N], [E,N], [E]).
+ * sorted_token_ids int32 [num_sorted]; expert_ids int32 [>= num_sorted / moe_block_size];
+ * num_tokens_past_padded int32 [1], read on the device; topk_weights fp32 [size_m * top_k].
+ * moe_block_size in {8, 16, 32, 48, 64}.
+ * -------------------------------------------------------------------------------------------- */
+int64_t marlin_b200_moe_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k,
+                                           int64_t top_k, int format);
+
+int marlin_b200_moe_gemm(const void* a, void* c, const int32_t* b_q_weight, const void* b_scales,
+                         const void* b_zeros, const void* b_bias, const float* global_scale,
+                         const int32_t* sorted_token_ids, const int32_t* expert_ids,
+                         const int32_t* num_tokens_past_padded, const float* topk_weights,
+                         int64_t num_sorted, int64_t num_experts, int moe_block_size, int top_k,
+                         int mul_topk_weights, int act_dtype, int format, int64_t size_m,
+                         int64_t size_n, int64_t size_k, int64_t num_groups, void* scratch,
+                         int64_t scratch_bytes, void* stream);
+
+/* ----------------------------------------------------------------------------------------------
+ * Token sorting for the grouped GEMM.  Stands in for
+ *   moe_align_block_size  csrc/moe/moe_align_sum_kernels.cu:477-569
+ * topk_ids int32 [numel] (flattened [tokens, top_k]); expert_map NULL or int32 [num_global_experts]
+ * (global -> local id, -1 = not on this rank; ids are looked up before counting).
+ * sorted_token_ids int32 [sorted_capacity] with sorted_capacity >= numel + num_experts*(block-1):
+ * per expert in ascending id its flat route indices in ascending order, padded with `numel` to a
+ * multiple of block_size; the tail is filled with `numel`.  expert_ids int32 [expert_ids_capacity]:
+ * expert of every block, tail -1.  num_tokens_post_pad int32 [1].
+ * The in-expert order is the stable ascending order of the reference's test oracle
+ * (tests/test_marlin_moe.py:194-213), deterministic for every size.
+ * scratch: at least marlin_b200_moe_align_scratch_bytes() bytes.
+ * -------------------------------------------------------------------------------------------- */
+int64_t marlin_b200_moe_align_scratch_bytes(int64_t numel, int64_t num_experts);
+
+int marlin_b200_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int64_t num_experts,
+                                     int64_t num_global_experts, int block_size,
+                                     const int32_t* expert_map, int32_t* sorted_token_ids,
+                                     int64_t sorted_capacity, int32_t* expert_ids,
+                                     int64_t expert_ids_capacity, int32_t* num_tokens_post_pad,
+                                     void* scratch, int64_t scratch_bytes, void* stream);
+
+/* ----------------------------------------------------------------------------------------------
+ * Fused softmax + top-k gating.  Stands in for
+ *   topk_softmax  csrc/moe/topk_softmax_kernels.cu:773-809
+ * gating [num_tokens, num_experts] of gating_dtype (MARLIN_B200_F16 / _BF16, or 2 = fp32);
+ * bias NULL or fp32 [num_experts], added to the probabilities for selection only.
+ * topk_weights fp32 [num_tokens, topk]; topk_indices int32 [num_tokens, topk];
+ * token_expert_indices int32 [num_tokens, topk] = j * num_tokens + t.  Ties pick the lower index.
+ * -------------------------------------------------------------------------------------------- */
+int marlin_b200_topk_softmax(const void* gating, int gating_dtype, const float* bias,
+                             float* topk_weights, int32_t* topk_indices,
+                             int32_t* token_expert_indices, int64_t num_tokens, int64_t num_experts,
+                             int topk, int renormalize, void* stream);
+
+/* ----------------------------------------------------------------------------------------------
+ * Glue of the two-GEMM expert layer (eager PyTorch in the reference,
+ * vllm/model_executor/layers/fused_moe/fused_marlin_moe.py:161-165,379-382).
+ * silu_and_mul: out[r, i] = silu(in[r, i]) * in[r, inter + i], in [rows, 2*inter], out [rows, inter].
+ * moe_sum     : out[t, :] = sum_j in[t * top_k + j, :], in [tokens * top_k, hidden].
+ * -------------------------------------------------------------------------------------------- */
+int marlin_b200_silu_and_mul(const void* in, void* out, int64_t rows, int64_t inter, int act_dtype,
+                             void* stream);
+int marlin_b200_moe_sum(const void* in, void* out, int64_t tokens, int top_k, int64_t hidden,
+                        int act_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MARLIN_B200_H_ */

@@ -1,0 +1,448 @@
+"""Host-side mirror of the reference's operator wrappers for the Marlin path.
+
+Same names, argument order and meaning as ``vllm/_custom_ops.py:1163-1321,2133-2169,2286-2301,
+2355-2425`` of the reference; failed argument checks raise ``RuntimeError`` with the reference's
+message fragments (``csrc/quantization/marlin/marlin.cu:83-506``,
+``csrc/moe/marlin_moe_wna16/ops.cu:102-529``).  Tensor-level checks (device, dtype, contiguity,
+shapes) live here; everything that only needs pointers and sizes is checked again inside the C ABI.
+Every launch goes to the current CUDA stream of the tensor's device; nothing synchronises."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .scalar_type import ScalarType, scalar_types
+
+_F16, _BF16 = 0, 1
+_SCALE_ACT, _SCALE_E4M3, _SCALE_E8M0 = 0, 1, 2
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _act_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float16:
+        return _F16
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise RuntimeError("unsupported `a` scalar_type: float16 or bfloat16 activations expected")
+
+
+def _type_id(b_q_type) -> int:
+    return int(b_q_type.id) if hasattr(b_q_type, "id") else int(b_q_type)
+
+
+def _resolve_format(b_type_id: int, b_scales: torch.Tensor, act_dtype: torch.dtype) -> int:
+    lib = _lib.load()
+    if b_type_id == scalar_types.float4_e2m1f.id:
+        if b_scales.dtype == torch.float8_e4m3fn:
+            kind = _SCALE_E4M3
+        elif b_scales.dtype == torch.float8_e8m0fnu:
+            kind = _SCALE_E8M0
+        else:
+            raise RuntimeError("When b_type = float4_e2m1f, b_scales must be float8_e4m3fn for NVFP4 "
+                               "or float8_e8m0fnu for MXFP4 scales.")
+    else:
+        kind = _SCALE_ACT
+        _check(b_scales.dtype == act_dtype,
+               "Marlin expects scales of the activation dtype, except FP4 uses float8_e4m3fn scales "
+               "for NVFP4 or float8_e8m0fnu scales for MXFP4.")
+    fmt = lib.marlin_b200_format_from_type_id(b_type_id, kind)
+    _check(fmt >= 0, "Marlin currently implements only uint4, uint4b8, uint8, uint8b128, fp8_e4m3fn, "
+                     "nvfp4, and mxfp4 dense weights.")
+    return fmt
+
+
+# --------------------------------------------------------------------------------------------
+# repack
+# --------------------------------------------------------------------------------------------
+
+def gptq_marlin_repack(b_q_weight: torch.Tensor, perm: torch.Tensor, size_k: int, size_n: int,
+                       num_bits: int, is_a_8bit: bool = False) -> torch.Tensor:
+    lib = _lib.load()
+    _check(not is_a_8bit, "is_a_8bit=True (8-bit activation layout) is not supported")
+    _check(num_bits in (4, 8), f"num_bits must be 4 or 8. Got = {num_bits}")
+    pf = 32 // num_bits
+    _check(b_q_weight.is_cuda, "b_q_weight is not on GPU")
+    _check(b_q_weight.is_contiguous(), "b_q_weight is not contiguous")
+    _check(b_q_weight.dtype == torch.int32, "b_q_weight type is not kInt")
+    _check(size_k % 16 == 0, f"size_k = {size_k} is not divisible by tile_k_size = 16")
+    _check(size_n % 64 == 0, f"size_n = {size_n} is not divisible by tile_n_size = 64")
+    _check(b_q_weight.dim() == 2 and b_q_weight.size(0) == size_k // pf and b_q_weight.size(1) == size_n,
+           f"Shape mismatch: b_q_weight = {tuple(b_q_weight.shape)}, size_k = {size_k}, "
+           f"size_n = {size_n}, pack_factor = {pf}")
+    has_perm = perm is not None and perm.numel() > 0
+    if has_perm:
+        _check(perm.is_cuda, "perm is not on GPU")
+        _check(perm.is_contiguous(), "perm is not contiguous")
+        _check(perm.dtype == torch.int32, "perm type is not at::kInt")
+        _check(perm.numel() == size_k, f"perm.numel() = {perm.numel()} is not size_k = {size_k}")
+    with torch.cuda.device(b_q_weight.device):
+        out = torch.empty((size_k // 16, size_n * 16 // pf), dtype=torch.int32, device=b_q_weight.device)
+        _lib.check(lib.marlin_b200_gptq_repack(_ptr(b_q_weight), _ptr(perm) if has_perm else None,
+                                               _ptr(out), size_k, size_n, num_bits,
+                                               _stream(b_q_weight.device)))
+    return out
+
+
+def awq_marlin_repack(b_q_weight: torch.Tensor, size_k: int, size_n: int, num_bits: int,
+                      is_a_8bit: bool = False) -> torch.Tensor:
+    lib = _lib.load()
+    _check(not is_a_8bit, "is_a_8bit=True (8-bit activation layout) is not supported")
+    _check(num_bits in (4, 8), f"num_bits must be 4 or 8. Got = {num_bits}")
+    pf = 32 // num_bits
+    _check(b_q_weight.is_cuda, "b_q_weight is not on GPU")
+    _check(b_q_weight.is_contiguous(), "b_q_weight is not contiguous")
+    _check(b_q_weight.dtype == torch.int32, "b_q_weight type is not kInt")
+    _check(size_k % 16 == 0, f"size_k = {size_k} is not divisible by tile_k_size = 16")
+    _check(size_n % 64 == 0, f"size_n = {size_n} is not divisible by tile_n_size = 64")
+    _check(b_q_weight.dim() == 2 and b_q_weight.size(0) == size_k and b_q_weight.size(1) == size_n // pf,
+           f"Shape mismatch: b_q_weight = {tuple(b_q_weight.shape)}, size_k = {size_k}, "
+           f"size_n = {size_n}, pack_factor = {pf}")
+    with torch.cuda.device(b_q_weight.device):
+        out = torch.empty((size_k // 16, size_n * 16 // pf), dtype=torch.int32, device=b_q_weight.device)
+        _lib.check(lib.marlin_b200_awq_repack(_ptr(b_q_weight), _ptr(out), size_k, size_n, num_bits,
+                                              _stream(b_q_weight.device)))
+    return out
+
+
+def gptq_marlin_moe_repack(b_q_weight: torch.Tensor, perm: torch.Tensor, size_k: int, size_n: int,
+                           num_bits: int, is_a_8bit: bool = False) -> torch.Tensor:
+    """Per-expert repack of ``[E, K/pf, N]`` (reference: vllm/_custom_ops.py:1228-1249)."""
+    e = b_q_weight.shape[0]
+    out = torch.empty((e, size_k // 16, size_n * (num_bits // 2)), dtype=b_q_weight.dtype,
+                      device=b_q_weight.device)
+    for i in range(e):
+        out[i] = gptq_marlin_repack(b_q_weight[i], perm[i] if perm is not None and perm.numel() else perm,
+                                    size_k, size_n, num_bits, is_a_8bit)
+    return out
+
+
+def awq_marlin_moe_repack(b_q_weight: torch.Tensor, perm: torch.Tensor | None, size_k: int, size_n: int,
+                          num_bits: int, is_a_8bit: bool = False) -> torch.Tensor:
+    """Per-expert repack of ``[E, K, N/pf]`` (reference: vllm/_custom_ops.py:1252-1269)."""
+    e = b_q_weight.shape[0]
+    out = torch.empty((e, size_k // 16, size_n * (num_bits // 2)), dtype=b_q_weight.dtype,
+                      device=b_q_weight.device)
+    for i in range(e):
+        out[i] = awq_marlin_repack(b_q_weight[i], size_k, size_n, num_bits, is_a_8bit)
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# dense GEMM
+# --------------------------------------------------------------------------------------------
+
+def _check_act_order_absent(g_idx, perm) -> None:
+    if g_idx is not None:
+        _check(g_idx.numel() == 0, "Marlin does not support act_order g_idx.")
+    if perm is not None:
+        _check(perm.numel() == 0, "Marlin does not support act_order perm.")
+
+
+def _scratch(nbytes: int, device: torch.device) -> torch.Tensor | None:
+    if nbytes <= 0:
+        return None
+    return torch.empty((nbytes,), dtype=torch.uint8, device=device)
+
+
+def marlin_gemm(a: torch.Tensor, c: torch.Tensor | None, b_q_weight: torch.Tensor,
+                b_bias: torch.Tensor | None, b_scales: torch.Tensor, a_scales: torch.Tensor | None,
+                global_scale: torch.Tensor | None, b_zeros: torch.Tensor | None,
+                g_idx: torch.Tensor | None, perm: torch.Tensor | None, workspace: torch.Tensor,
+                b_q_type: ScalarType | int, size_m: int, size_n: int, size_k: int,
+                is_k_full: bool = True, use_atomic_add: bool = False, use_fp32_reduce: bool = False,
+                is_zp_float: bool = False) -> torch.Tensor:
+    """C[size_m, size_n] = a @ dequant(b_q_weight).  ``workspace``, ``is_k_full``, ``use_atomic_add``
+    and ``use_fp32_reduce`` are accepted and ignored, as in the reference (marlin.cu:103-106); the
+    split-K scratch is allocated here from torch's caching allocator and the caller's workspace is
+    never touched."""
+    lib = _lib.load()
+    _check_act_order_absent(g_idx, perm)
+    _check(a_scales is None, "a_scales can only be used for 8bit activation.")
+    act = _act_code(a.dtype)
+    b_type_id = _type_id(b_q_type)
+    fmt = _resolve_format(b_type_id, b_scales, a.dtype)
+    pf = 8 if fmt in (0, 1, 5, 6) else 4
+
+    _check(a.dim() == 2, "a must be 2-D")
+    _check(a.size(0) == size_m, f"Shape mismatch: a.size(0) = {a.size(0)}, size_m = {size_m}")
+    _check(a.size(1) == size_k, f"Shape mismatch: a.size(1) = {a.size(1)}, size_k = {size_k}")
+    _check(size_k % 16 == 0, f"size_k = {size_k} is not divisible by tile_size = 16")
+    _check(b_q_weight.dim() == 2 and size_k // 16 == b_q_weight.size(0),
+           f"Shape mismatch: b_q_weight.size(0) = {b_q_weight.size(0)}, size_k = {size_k}, tile_size = 16")
+    _check(b_q_weight.size(1) % 16 == 0,
+           f"b_q_weight.size(1) = {b_q_weight.size(1)} is not divisible by tile_size = 16")
+    actual_n = (b_q_weight.size(1) // 16) * pf
+    _check(size_n == actual_n, f"size_n = {size_n}, actual_size_n = {actual_n}")
+    _check(a.is_cuda, "A is not on GPU")
+    _check(a.stride(1) == 1, "A.stride(1) is not 1")
+    _check(a.stride(0) % 8 == 0, "A.stride(0) must divisible by 8")
+    _check(a.data_ptr() % 16 == 0, "A must aligned to 16 bytes")
+    _check(b_q_weight.is_cuda, "b_q_weight is not on GPU")
+    _check(b_q_weight.is_contiguous(), "b_q_weight is not contiguous")
+    _check(b_q_weight.dtype == torch.int32, "Marlin expects int32 packed weights.")
+    _check(b_scales.is_cuda, "b_scales is not on GPU")
+    _check(b_scales.is_contiguous(), "b_scales is not contiguous")
+
+    with torch.cuda.device(a.device):
+        if c is not None:
+            _check(c.is_cuda, "c is not on GPU")
+            _check(c.is_contiguous(), "c is not contiguous")
+            _check(c.dtype == a.dtype, "scalar type of a must be the same with c for 16 bit activation")
+            _check(c.size(0) == size_m, f"Shape mismatch: c.size(0) = {c.size(0)}, size_m = {size_m}")
+            _check(c.size(1) == size_n, f"Shape mismatch: c.size(1) = {c.size(1)}, size_n = {size_n}")
+        else:
+            c = torch.empty((size_m, size_n), dtype=a.dtype, device=a.device)
+        if size_m == 0:
+            return c
+
+        _check(b_scales.dim() == 2, f"b_scales rank = {b_scales.dim()} is not 2")
+        _check(b_scales.size(1) == size_n, f"b_scales dim 1 = {b_scales.size(1)} is not size_n = {size_n}")
+        num_groups = b_scales.size(0)
+        if num_groups > 1:
+            _check(size_k % num_groups == 0,
+                   f"size_k = {size_k}, is not divisible by b_scales.size(0) = {num_groups}")
+
+        if global_scale is not None:
+            _check(fmt == 5, "Marlin supports global_scale only for nvfp4 format.")
+            _check(global_scale.is_cuda, "global_scale is not on GPU")
+            _check(global_scale.is_contiguous(), "global_scale is not contiguous")
+            _check(global_scale.dtype == torch.float32, "Marlin nvfp4 expects fp32 global_scale.")
+            _check(global_scale.numel() == 1, "Marlin nvfp4 expects a single global_scale value.")
+        else:
+            _check(fmt != 5, "the global_scale parameter must be passed for nvfp4 format.")
+
+        if b_bias is not None:
+            _check(b_bias.is_cuda, "b_bias is not on GPU")
+            _check(b_bias.is_contiguous(), "b_bias is not contiguous")
+            _check(b_bias.dtype == a.dtype, "Marlin bias must have the activation dtype.")
+            _check(b_bias.size(0) == size_n, "b_bias.size(0) != size_n")
+
+        has_zp = b_zeros is not None and b_zeros.size(-1) > 0
+        _check(not has_zp or fmt in (1, 3),
+               "Marlin does not support zero-point metadata for this quant type.")
+        if has_zp:
+            _check(b_zeros.is_cuda, "b_zeros is not on GPU")
+            _check(b_zeros.is_contiguous(), "b_zeros is not contiguous")
+            _check(is_zp_float, "Marlin received b_zeros but is_zp_float is false. Packed integer "
+                                "zero-points are not supported on the dense uint4/uint8 path.")
+            _check(b_zeros.dim() == 2, f"b_zeros rank = {b_zeros.dim()} is not 2")
+            _check(b_zeros.dtype == a.dtype, "Marlin uint4/uint8 dense path expects zero points of the "
+                                             "activation dtype.")
+            _check(b_zeros.size(1) == size_n, f"b_zeros dim 1 = {b_zeros.size(1)} is not size_n = {size_n}")
+            _check(b_zeros.size(0) == num_groups,
+                   f"b_zeros dim 0 = {b_zeros.size(0)} is not num_groups = {num_groups}")
+        else:
+            _check(not is_zp_float, "is_zp_float is true but b_zeros was not provided.")
+            _check(fmt not in (1, 3), "Marlin uint4/uint8 dense path requires float zero points.")
+
+        nbytes = lib.marlin_b200_gemm_scratch_bytes(size_m, size_n, size_k, fmt)
+        scratch = _scratch(nbytes, a.device)
+        _lib.check(lib.marlin_b200_gemm(
+            _ptr(a), _ptr(c), _ptr(b_q_weight), _ptr(b_scales), _ptr(b_zeros) if has_zp else None,
+            _ptr(b_bias), _ptr(global_scale), act, fmt, size_m, size_n, size_k, a.stride(0), num_groups,
+            _ptr(scratch), nbytes, _stream(a.device)))
+    return c
+
+
+# --------------------------------------------------------------------------------------------
+# MoE
+# --------------------------------------------------------------------------------------------
+
+def moe_wna16_marlin_gemm(input: torch.Tensor, output: torch.Tensor | None, b_qweight: torch.Tensor,
+                          b_bias: torch.Tensor | None, b_scales: torch.Tensor,
+                          a_scales: torch.Tensor | None, global_scale: torch.Tensor | None,
+                          b_qzeros: torch.Tensor | None, g_idx: torch.Tensor | None,
+                          perm: torch.Tensor | None, workspace: torch.Tensor,
+                          sorted_token_ids: torch.Tensor, expert_ids: torch.Tensor,
+                          num_tokens_past_padded: torch.Tensor, topk_weights: torch.Tensor,
+                          moe_block_size: int, top_k: int, mul_topk_weights: bool,
+                          b_q_type: ScalarType | int, size_m: int, size_n: int, size_k: int,
+                          is_k_full: bool = True, use_atomic_add: bool = False,
+                          use_fp32_reduce: bool = False, is_zp_float: bool = False, thread_k: int = -1,
+                          thread_n: int = -1, blocks_per_sm: int = -1) -> torch.Tensor:
+    """Grouped expert GEMM; rows follow ``sorted_token_ids`` (flat route ids ``t * top_k + j``).
+    Ignored arguments as in the reference (ops.cu:126-132)."""
+    lib = _lib.load()
+    _check_act_order_absent(g_idx, perm)
+    _check(a_scales is None, "a_scales can only be used for 8bit activation.")
+    a = input
+    act = _act_code(a.dtype)
+    b_type_id = _type_id(b_q_type)
+    fmt = _resolve_format(b_type_id, b_scales, a.dtype)
+    pf = 8 if fmt in (0, 1, 5, 6) else 4
+    if moe_block_size != 8:
+        _check(moe_block_size % 16 == 0 and 16 <= moe_block_size <= 64,
+               f"unsupported moe_block_size={moe_block_size}")
+    _check(a.size(0) == size_m, f"Shape mismatch: a.size(0) = {a.size(0)}, size_m = {size_m}")
+    _check(a.size(1) == size_k, f"Shape mismatch: a.size(1) = {a.size(1)}, size_k = {size_k}")
+    _check(size_k % 16 == 0, f"size_k = {size_k} is not divisible by tile_size = 16")
+    _check(b_qweight.dim() == 3, "b_q_weight must be [experts, size_k / 16, size_n * 16 / pack_factor]")
+    num_experts = b_qweight.size(0)
+    _check(size_k // 16 == b_qweight.size(1),
+           f"Shape mismatch: b_q_weight.size(1) = {b_qweight.size(1)}, size_k = {size_k}, tile_size = 16")
+    _check(b_qweight.size(2) % 16 == 0,
+           f"b_q_weight.size(2) = {b_qweight.size(2)} is not divisible by tile_size = 16")
+    actual_n = (b_qweight.size(2) // 16) * pf
+    _check(size_n == actual_n, f"size_n = {size_n}, actual_size_n = {actual_n}")
+    _check(a.is_cuda, "A is not on GPU")
+    _check(a.is_contiguous(), "A is not contiguous")
+    _check(b_qweight.is_cuda, "b_q_weight is not on GPU")
+    _check(b_qweight.is_contiguous(), "b_q_weight is not contiguous")
+    _check(b_qweight.dtype == torch.int32, "Marlin expects int32 packed weights.")
+    _check(b_scales.is_cuda, "b_scales is not on GPU")
+    _check(b_scales.is_contiguous(), "b_scales is not contiguous")
+
+    with torch.cuda.device(a.device):
+        if output is not None:
+            c = output
+            _check(c.is_cuda, "c is not on GPU")
+            _check(c.is_contiguous(), "c is not contiguous")
+            _check(c.dtype == a.dtype, "scalar type of a must be the same with c for 16 bit activation")
+            _check(c.size(0) == size_m * top_k,
+                   f"Shape mismatch: c.size(0) = {c.size(0)}, size_m * topk = {size_m * top_k}")
+            _check(c.size(1) == size_n, f"Shape mismatch: c.size(1) = {c.size(1)}, size_n = {size_n}")
+        else:
+            c = torch.empty((size_m * top_k, size_n), dtype=a.dtype, device=a.device)
+
+        _check(b_scales.dim() == 3, f"b_scales rank = {b_scales.dim()} is not 3")
+        _check(b_scales.size(0) == num_experts, "b_scales dim 0 is not the number of experts")
+        _check(b_scales.size(2) == size_n, f"b_scales dim 2 = {b_scales.size(2)} is not size_n = {size_n}")
+        num_groups = b_scales.size(1)
+        if num_groups > 1:
+            _check(size_k % num_groups == 0,
+                   f"size_k = {size_k}, is not divisible by b_scales.size(1) = {num_groups}")
+
+        if global_scale is not None:
+            _check(fmt == 5, "Marlin MoE supports global_scale only for nvfp4 format.")
+            _check(global_scale.is_cuda and global_scale.is_contiguous(), "global_scale is not on GPU")
+            _check(global_scale.dtype == torch.float32, "Marlin MoE nvfp4 expects fp32 global_scale.")
+            _check(global_scale.numel() == num_experts,
+                   "Marlin MoE nvfp4 expects global_scale numel = num_experts. Got global_scale.numel() = "
+                   f"{global_scale.numel()}, num_experts = {num_experts}")
+        else:
+            _check(fmt != 5, "the global_scale parameter must be passed for nvfp4 format.")
+
+        if b_bias is not None:
+            _check(b_bias.is_cuda and b_bias.is_contiguous(), "b_bias is not on GPU")
+            _check(b_bias.dtype == a.dtype, "Marlin bias must have the activation dtype.")
+            _check(b_bias.dim() == 2 and b_bias.size(0) == num_experts and b_bias.size(1) == size_n,
+                   "b_bias must be [experts, size_n]")
+
+        has_zp = b_qzeros is not None and b_qzeros.size(-1) > 0
+        _check(not has_zp or fmt in (1, 3),
+               "Marlin does not support zero-point metadata for this quant type.")
+        if has_zp:
+            _check(b_qzeros.is_cuda and b_qzeros.is_contiguous(), "b_zeros is not on GPU")
+            _check(is_zp_float, "Marlin MoE received b_zeros but is_zp_float is false. Packed integer "
+                                "zero-points are not supported.")
+            _check(b_qzeros.dtype == a.dtype, "Marlin MoE expects zero points of the activation dtype.")
+            _check(tuple(b_qzeros.shape) == (num_experts, num_groups, size_n),
+                   "b_zeros must be [experts, num_groups, size_n]")
+        else:
+            _check(not is_zp_float, "is_zp_float is true but b_zeros was not provided.")
+            _check(fmt not in (1, 3), "Marlin uint4/uint8 MoE path requires float zero points.")
+
+        for t, name in ((sorted_token_ids, "sorted_token_ids"), (expert_ids, "expert_ids"),
+                        (num_tokens_past_padded, "num_tokens_past_padded")):
+            _check(t.is_cuda and t.is_contiguous(), f"{name} must be a contiguous GPU tensor")
+            _check(t.dtype == torch.int32, f"{name} must be int32")
+        _check(topk_weights.is_cuda and topk_weights.is_contiguous() and topk_weights.dtype == torch.float32,
+               "topk_weights must be a contiguous fp32 GPU tensor")
+        _check(topk_weights.numel() >= size_m * top_k, "topk_weights has fewer than size_m * top_k entries")
+        num_sorted = sorted_token_ids.numel()
+
+        nbytes = lib.marlin_b200_moe_gemm_scratch_bytes(size_m, size_n, size_k, top_k, fmt)
+        scratch = _scratch(nbytes, a.device)
+        _lib.check(lib.marlin_b200_moe_gemm(
+            _ptr(a), _ptr(c), _ptr(b_qweight), _ptr(b_scales), _ptr(b_qzeros) if has_zp else None,
+            _ptr(b_bias), _ptr(global_scale), _ptr(sorted_token_ids), _ptr(expert_ids),
+            _ptr(num_tokens_past_padded), _ptr(topk_weights), num_sorted, num_experts,
+            moe_block_size, top_k, int(bool(mul_topk_weights)), act, fmt, size_m, size_n, size_k,
+            num_groups, _ptr(scratch), nbytes, _stream(a.device)))
+    return c
+
+
+def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: int,
+                         sorted_token_ids: torch.Tensor, experts_ids: torch.Tensor,
+                         num_tokens_post_pad: torch.Tensor,
+                         expert_map: torch.Tensor | None = None) -> None:
+    """Fills the three caller-allocated outputs (reference: moe_align_sum_kernels.cu:477-569)."""
+    lib = _lib.load()
+    _check(topk_ids.is_cuda and topk_ids.is_contiguous(), "topk_ids must be a contiguous GPU tensor")
+    _check(topk_ids.dtype == torch.int32, "topk_ids must be int32")
+    for t in (sorted_token_ids, experts_ids, num_tokens_post_pad):
+        _check(t.is_cuda and t.is_contiguous() and t.dtype == torch.int32,
+               "align outputs must be contiguous int32 GPU tensors")
+    num_global = 0
+    if expert_map is not None:
+        _check(expert_map.is_cuda and expert_map.is_contiguous() and expert_map.dtype == torch.int32,
+               "expert_map must be a contiguous int32 GPU tensor")
+        num_global = expert_map.numel()
+    numel = topk_ids.numel()
+    with torch.cuda.device(topk_ids.device):
+        nbytes = lib.marlin_b200_moe_align_scratch_bytes(numel, num_experts)
+        scratch = _scratch(nbytes, topk_ids.device)
+        _lib.check(lib.marlin_b200_moe_align_block_size(
+            _ptr(topk_ids), numel, num_experts, num_global, block_size, _ptr(expert_map),
+            _ptr(sorted_token_ids), sorted_token_ids.numel(), _ptr(experts_ids), experts_ids.numel(),
+            _ptr(num_tokens_post_pad), _ptr(scratch), nbytes, _stream(topk_ids.device)))
+
+
+def topk_softmax(topk_weights: torch.Tensor, topk_ids: torch.Tensor, token_expert_indices: torch.Tensor,
+                 gating_output: torch.Tensor, renormalize: bool = False,
+                 e_score_correction_bias: torch.Tensor | None = None) -> None:
+    """Fused softmax + top-k (reference: topk_softmax_kernels.cu:773-809)."""
+    lib = _lib.load()
+    _check(gating_output.is_cuda and gating_output.is_contiguous(), "gating_output must be contiguous on GPU")
+    code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}.get(gating_output.dtype)
+    _check(code is not None, "Invalid gating_output type")
+    _check(topk_weights.dtype == torch.float32 and topk_weights.is_contiguous(), "topk_weights must be fp32")
+    _check(topk_ids.dtype == torch.int32 and topk_ids.is_contiguous(), "topk_indices must be int32")
+    _check(token_expert_indices.dtype == torch.int32 and token_expert_indices.is_contiguous(),
+           "token_expert_indices must be int32")
+    num_experts = gating_output.size(-1)
+    num_tokens = gating_output.numel() // max(num_experts, 1)
+    topk = topk_weights.size(-1)
+    bias = e_score_correction_bias
+    if bias is not None:
+        _check(bias.is_cuda and bias.is_contiguous() and bias.dtype == torch.float32 and
+               bias.numel() == num_experts, "bias must be a contiguous fp32 [num_experts] GPU tensor")
+    with torch.cuda.device(gating_output.device):
+        _lib.check(lib.marlin_b200_topk_softmax(
+            _ptr(gating_output), code, _ptr(bias), _ptr(topk_weights), _ptr(topk_ids),
+            _ptr(token_expert_indices), num_tokens, num_experts, topk, int(bool(renormalize)),
+            _stream(gating_output.device)))
+
+
+def silu_and_mul(out: torch.Tensor, x: torch.Tensor) -> None:
+    """out = silu(x[..., :d]) * x[..., d:] (reference: fused_moe/activation.py:45-67, eager there)."""
+    lib = _lib.load()
+    _check(x.is_cuda and x.is_contiguous() and out.is_contiguous(), "silu_and_mul needs contiguous GPU tensors")
+    inter = x.size(-1) // 2
+    rows = x.numel() // max(x.size(-1), 1)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.marlin_b200_silu_and_mul(_ptr(x), _ptr(out), rows, inter, _act_code(x.dtype),
+                                                _stream(x.device)))
+
+
+def moe_sum(input: torch.Tensor, output: torch.Tensor) -> None:
+    """output[t] = sum_j input[t, j] for input [tokens, top_k, hidden]
+    (reference: fused_marlin_moe.py:379-382, torch.sum there)."""
+    lib = _lib.load()
+    _check(input.is_cuda and input.is_contiguous() and output.is_contiguous(), "moe_sum needs contiguous GPU tensors")
+    tokens, top_k, hidden = input.shape
+    with torch.cuda.device(input.device):
+        _lib.check(lib.marlin_b200_moe_sum(_ptr(input), _ptr(output), tokens, top_k, hidden,
+                                           _act_code(input.dtype), _stream(input.device)))

@@ -1,0 +1,154 @@
+"""Dense marlin_gemm parity against dequantise -> fp32 matmul (the oracle), through the C ABI.
+
+Tolerance (stated by the task): mean|y - ref| / mean|ref| <= 1e-2 and max|y - ref| <= 5e-2 * max|ref|."""
+import pytest
+import torch
+
+from oracle import marlin_oracle as mo
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+MEAN_TOL, MAX_TOL = 1e-2, 5e-2
+
+
+def _ops():
+    from marlin_v100_b200 import ops
+    return ops
+
+
+def run_gemm(a, qw, bias=None, c=None):
+    ops = _ops()
+    d = util.to_dev(qw)
+    ws = torch.empty(0, dtype=torch.int32, device="cuda")
+    out = ops.marlin_gemm(a.cuda(), c, d.packed, None if bias is None else mo.permute_bias(bias).cuda(),
+                          d.scales, None, d.global_scale, d.zeros, None, None, ws, qw.type_id,
+                          a.shape[0], qw.size_n, qw.size_k, True, False, True, qw.zeros is not None)
+    assert ws.numel() == 0
+    return out
+
+
+def check(out, ref):
+    assert torch.isfinite(out.float()).all()
+    mre, mxe = mo.mean_rel_err(out.cpu(), ref), mo.max_abs_err_frac(out.cpu(), ref)
+    assert mre <= MEAN_TOL and mxe <= MAX_TOL, f"mean_rel={mre:.3e} max_frac={mxe:.3e}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("fmt", util.FORMATS)
+@pytest.mark.parametrize("m", [1, 16])
+def test_formats_small(fmt, dtype, m):
+    a, qw = util.make_dense(m, 512, 512, fmt, dtype, seed=1)
+    out = run_gemm(a, qw)
+    assert out.dtype == dtype and tuple(out.shape) == (m, 512)
+    check(out, mo.dense_reference(a, qw.deq))
+
+
+@pytest.mark.parametrize("fmt,gs", [("u4b8", -1), ("u4b8", 32), ("u4b8", 64), ("u4", -1), ("u4", 64),
+                                    ("u8b128", -1), ("u8b128", 128), ("u8", 32), ("fp8", -1), ("fp8", 128)])
+def test_group_sizes(fmt, gs):
+    a, qw = util.make_dense(8, 256, 256, fmt, torch.float16, group_size=gs, seed=2)
+    check(run_gemm(a, qw), mo.dense_reference(a, qw.deq))
+
+
+@pytest.mark.parametrize("m", [1, 2, 7, 8, 9, 15, 16, 17, 24, 33, 48, 64, 100, 128, 257])
+def test_odd_m(m):
+    a, qw = util.make_dense(m, 512, 768, "u4b8", torch.float16, seed=3)
+    check(run_gemm(a, qw), mo.dense_reference(a, qw.deq))
+
+
+@pytest.mark.parametrize("n", [64, 128, 192, 256, 320, 384, 640, 832, 1152])
+@pytest.mark.parametrize("fmt", ["u4b8", "u8b128", "mxfp4"])
+def test_alignment_n(n, fmt):
+    a, qw = util.make_dense(5, 256, n, fmt, torch.float16, seed=4)
+    check(run_gemm(a, qw), mo.dense_reference(a, qw.deq))
+
+
+@pytest.mark.parametrize("k", [32, 64, 96, 160, 2048 + 32])
+def test_short_and_ragged_k(k):
+    a, qw = util.make_dense(4, k, 256, "u4b8", torch.float16, group_size=32, seed=5)
+    check(run_gemm(a, qw), mo.dense_reference(a, qw.deq))
+
+
+@pytest.mark.parametrize("fmt", ["u4b8", "u4", "nvfp4"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_bias(fmt, dtype):
+    a, qw = util.make_dense(6, 256, 512, fmt, dtype, seed=6)
+    bias = (torch.randn(512, generator=torch.Generator().manual_seed(7)) * 0.5).to(dtype)
+    check(run_gemm(a, qw, bias=bias), mo.dense_reference(a, qw.deq, bias))
+
+
+def test_config1_shape_fp16_u4b8():
+    # first configuration of the headline benchmark: M=16, K=N=4096, group 128, seed 0
+    a, qw = util.make_dense(16, 4096, 4096, "u4b8", torch.float16, seed=0)
+    check(run_gemm(a, qw), mo.dense_reference(a, qw.deq))
+
+
+def test_strided_a_and_preallocated_c():
+    a, qw = util.make_dense(4, 256, 256, "u4b8", torch.float16, seed=8)
+    big = torch.zeros(4, 512, dtype=torch.float16, device="cuda")
+    big[:, :256] = a.cuda()
+    av = big[:, :256]
+    ops = _ops()
+    d = util.to_dev(qw)
+    c = torch.full((4, 256), 7.0, dtype=torch.float16, device="cuda")
+    ws = torch.empty(0, dtype=torch.int32, device="cuda")
+    out = ops.marlin_gemm(av, c, d.packed, None, d.scales, None, None, None, None, None, ws, qw.type_id,
+                          4, 256, 256)
+    assert out.data_ptr() == c.data_ptr()
+    check(out, mo.dense_reference(a, qw.deq))
+
+
+def test_m_zero_returns_empty():
+    a, qw = util.make_dense(1, 64, 64, "u4b8", torch.float16, group_size=32, seed=9)
+    d = util.to_dev(qw)
+    ops = _ops()
+    out = ops.marlin_gemm(a.cuda()[:0], None, d.packed, None, d.scales, None, None, None, None, None,
+                          torch.empty(0, dtype=torch.int32, device="cuda"), qw.type_id, 0, 64, 64)
+    assert tuple(out.shape) == (0, 64)
+
+
+def test_linearity_full_size():
+    """Size-independent property at a full benchmark shape: the op is linear in A."""
+    k, n = 8192, 28672
+    g = torch.Generator().manual_seed(11)
+    q = torch.randint(0, 16, (k, n), generator=g, dtype=torch.int32)
+    packed = mo.marlin_pack(q, 4).cuda()
+    scales = (torch.rand(k // 128, n, generator=g) * 0.01 + 0.001).to(torch.bfloat16).cuda()
+    zeros = (torch.rand(k // 128, n, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    a1 = torch.randn(16, k, generator=g).to(torch.bfloat16)
+    a2 = torch.randn(16, k, generator=g).to(torch.bfloat16)
+    ops = _ops()
+    ws = torch.empty(0, dtype=torch.int32, device="cuda")
+
+    def f(a):
+        return ops.marlin_gemm(a.cuda(), None, packed, None, scales, None, None, zeros, None, None, ws,
+                               mo.TYPE_U4, 16, n, k, True, False, True, True).float()
+
+    y1, y2, y12 = f(a1), f(a2), f((a1.float() + a2.float()).to(torch.bfloat16))
+    ref = y1 + y2
+    # a1 + a2 is rounded to bf16 before the call: allow that rounding on top of the output rounding
+    assert mo.mean_rel_err(y12.cpu(), ref.cpu()) < 2e-2
+    # run-to-run determinism (the split-K reduction is ordered)
+    assert torch.equal(f(a1), y1)
+
+
+@pytest.mark.parametrize("kw,match", [
+    (dict(g_idx=True), "does not support act_order g_idx"),
+    (dict(perm=True), "does not support act_order perm"),
+    (dict(size_n=100), "size_n = 100, actual_size_n"),
+    (dict(size_m=3), "Shape mismatch: a.size"),
+    (dict(zp_on_b8=True), "does not support zero-point"),
+])
+def test_argument_errors(kw, match):
+    a, qw = util.make_dense(2, 64, 64, "u4b8", torch.float16, group_size=32, seed=10)
+    d = util.to_dev(qw)
+    ops = _ops()
+    one = torch.ones(4, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match=match):
+        ops.marlin_gemm(a.cuda(), None, d.packed, None, d.scales, None, None,
+                        d.scales if kw.get("zp_on_b8") else None,
+                        one if kw.get("g_idx") else None, one if kw.get("perm") else None,
+                        torch.empty(0, dtype=torch.int32, device="cuda"), qw.type_id,
+                        kw.get("size_m", 2), kw.get("size_n", 64), 64, True, False, True,
+                        bool(kw.get("zp_on_b8")))
