@@ -51,6 +51,10 @@ const char* marlin_b200_last_error(void);
 /* Library version, "major.minor". */
 const char* marlin_b200_version(void);
 
+/* Number of kernels this library has launched in this process so far (all entry points, all
+ * threads).  Diagnostics only; it has no counterpart in the reference. */
+int64_t marlin_b200_launch_count(void);
+
 /* Maps (b_type_id, scale kind) to a MARLIN_B200_FMT_* value, or -1.
  * Stands in for the b_type routing of csrc/quantization/marlin/marlin.cu:142-183,385-505. */
 int marlin_b200_format_from_type_id(int64_t b_type_id, int scale_kind);

@@ -1,5 +1,6 @@
 // C ABI entry points of the GEMM paths: argument checks (the conditions the reference enforces with
 // TORCH_CHECK in marlin.cu / ops.cu, restated for raw pointers) and kernel selection.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -18,6 +19,11 @@ void set_error(const char* fmt, ...) {
   vsnprintf(g_error, sizeof(g_error), fmt, ap);
   va_end(ap);
 }
+
+namespace {
+std::atomic<int64_t> g_launches{0};
+}
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 int sm_count() {
   static int cached[64] = {};
@@ -105,6 +111,7 @@ using namespace mb200;
 
 extern "C" const char* marlin_b200_last_error(void) { return g_error; }
 extern "C" const char* marlin_b200_version(void) { return "0.1"; }
+extern "C" int64_t marlin_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int marlin_b200_format_from_type_id(int64_t id, int scale_kind) {
   if (id == kIdU4B8) return kU4B8;

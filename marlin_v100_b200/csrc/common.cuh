@@ -30,6 +30,7 @@ __host__ __device__ constexpr bool format_scale_is_byte(int f) { return f == kNV
 // Host-side error plumbing (abi.cu owns the storage).
 void set_error(const char* fmt, ...);
 int sm_count();  // SMs of the current device, cached
+void count_launches(int n);  // bumps the process-wide kernel launch counter
 
 #define MB_CHECK(cond, ...)             \
   do {                                  \

@@ -90,20 +90,20 @@ template <typename T, bool ZERO_C>
 __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   if constexpr (kIsHalf<T>) {
     if constexpr (ZERO_C)
-      asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                    : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                    : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
     else
-      asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                    : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                    : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   } else {
     if constexpr (ZERO_C)
-      asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                    : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                    : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
     else
-      asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                    : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                    : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
@@ -260,17 +260,13 @@ __device__ __forceinline__ void fixup(float (&dst)[8][MB][4], const float (&src)
     }
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb) {
-      float v0 = s0 * src[q][mb][0], v1 = s0 * src[q][mb][1], v2 = s1 * src[q][mb][2], v3 = s1 * src[q][mb][3];
-      if constexpr (needs_act_sum<T, FMT>()) {
-        v0 = fmaf(-c0, asum[mb][0], v0);
-        v1 = fmaf(-c0, asum[mb][1], v1);
-        v2 = fmaf(-c1, asum[mb][0], v2);
-        v3 = fmaf(-c1, asum[mb][1], v3);
-      }
-      if constexpr (ACCUMULATE) {
-        dst[q][mb][0] += v0; dst[q][mb][1] += v1; dst[q][mb][2] += v2; dst[q][mb][3] += v3;
-      } else {
-        dst[q][mb][0] = v0; dst[q][mb][1] = v1; dst[q][mb][2] = v2; dst[q][mb][3] = v3;
+      const float sv[4] = {s0, s0, s1, s1};
+      const float cv[4] = {c0, c0, c1, c1};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float v = ACCUMULATE ? fmaf(sv[i], src[q][mb][i], dst[q][mb][i]) : sv[i] * src[q][mb][i];
+        if constexpr (needs_act_sum<T, FMT>()) v = fmaf(-cv[i], asum[mb][i & 1], v);
+        dst[q][mb][i] = v;
       }
     }
   }
@@ -333,16 +329,18 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     // ---------------- producer ----------------
     if (lane == 0) {
       constexpr int ROWS_PER_KT = (BITS == 4) ? 16 : 32;  // 128-byte rows of one k-tile per group
-      int it = 0;
-      for (int64_t u = u0; u < u1; ++u, ++it) {
-        const int s = it % STAGES;
+      int g = (int)(u0 / p.kc);
+      int c = (int)(u0 - (int64_t)g * p.kc);
+      const int total = (int)(u1 - u0);
+      int s = 0;
+      uint32_t phase = 0;
+      for (int it = 0; it < total; ++it) {
         if (it >= STAGES) {
-          if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, &s_abort)) {
+          if (!mbar_wait(empty_bar(s), phase ^ 1u, &s_abort)) {
             atomicExch(&g_decode_status, 1);
             break;
           }
         }
-        const int g = (int)(u / p.kc), c = (int)(u % p.kc);
         const uint32_t st = base + s * L::BYTES;
         mbar_arrive_expect_tx(full_bar(s), p.tx_bytes);
         tma_load_3d(st, &tmW, full_bar(s), 0, g * ROWS_PER_KT, c * KT_PER_CHUNK);
@@ -352,6 +350,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           tma_load_2d(st + L::OFF_S, &tmS, full_bar(s), g * GROUP_N, srow);
           if constexpr (format_has_zp(FMT)) tma_load_2d(st + L::OFF_Z, &tmZ, full_bar(s), g * GROUP_N, srow);
         }
+        if (++c == p.kc) { c = 0; ++g; }
+        if (++s == STAGES) { s = 0; phase ^= 1u; }
       }
     }
     return;
@@ -362,39 +362,63 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const int pair = warp >> 1, parity = warp & 1;
   const int p_lane = ((gid >> 1) & 1) ^ parity;
   constexpr int SROW_BYTES = format_scale_is_byte(FMT) ? GROUP_N : GROUP_N * 2;
+  const uint8_t* const smem = smem_raw + (base - smem_u32(smem_raw));  // generic pointer to `base`
+
+  // per-thread byte offsets inside a stage (the 128-byte swizzle folded in)
+  int woff[BITS == 4 ? 4 : 8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int lk = 2 * t + (i & 1) + ((i >> 1) << 3);
+    if constexpr (BITS == 4) {
+      woff[i] = lk * 128 + ((gid ^ (lk & 7)) << 4) + p_lane * 8;
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int R = lk * 2 + h;
+        woff[h * 4 + i] = R * 128 + ((gid ^ (R & 7)) << 4) + p_lane * 8;
+      }
+    }
+  }
+  int aoff[MB];
+#pragma unroll
+  for (int mb = 0; mb < MB; ++mb) aoff[mb] = L::OFF_A + (mb * 8 + gid) * 128 + t * 4;
 
   float acc[8][MB][4];
   float tmp[(POST && SCOPE > 0) ? 8 : 1][MB][4];
   float asum[MB][4];
-  int64_t seg_first = u0;
-  int it = 0;
   bool alive = true;
 
-  for (int64_t u = u0; u < u1; ++u, ++it) {
-    const int s = it % STAGES;
-    const int g = (int)(u / p.kc), c = (int)(u % p.kc);
-    if (u == u0 || c == 0) {
-      seg_first = u;
+  // walk the CTA's range segment by segment (a segment = consecutive chunks of one column group)
+  int g = (int)(u0 / p.kc);
+  int c0 = (int)(u0 - (int64_t)g * p.kc);
+  const int total = (int)(u1 - u0);
+  int it0 = 0;                       // index (inside the range) of the segment's first chunk
+  int own = pair;                    // next chunk index this pair owns
+  int stage = pair % STAGES;         // its stage and barrier phase
+  uint32_t phase = 0;
+  bool first_segment = true;
+
+  while (it0 < total) {
+    const int seg_len = min(p.kc - c0, total - it0);
 #pragma unroll
-      for (int q = 0; q < 8; ++q)
-#pragma unroll
-        for (int mb = 0; mb < MB; ++mb)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) acc[q][mb][i] = 0.f;
+    for (int q = 0; q < 8; ++q)
 #pragma unroll
       for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) asum[mb][i] = 0.f;
-    }
+        for (int i = 0; i < 4; ++i) acc[q][mb][i] = 0.f;
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) asum[mb][i] = 0.f;
 
-    if ((it & (PAIRS - 1)) == pair) {
-      // After a wait gave up the warp keeps walking its units (so that the CTA-wide barriers below
+    for (; own < it0 + seg_len; own += PAIRS) {
+      // After a wait gave up the warp keeps walking its chunks (so that the CTA-wide barriers below
       // still meet) but no longer waits for, reads or writes any data.
-      if (alive && !mbar_wait(full_bar(s), (it / STAGES) & 1, &s_abort)) {
+      if (alive && !mbar_wait(full_bar(stage), phase, &s_abort)) {
         atomicExch(&g_decode_status, 2);
         alive = false;
       }
-      const uint32_t st = base + s * L::BYTES;
+      const uint8_t* st = smem + stage * L::BYTES;
       if (alive) {
 #pragma unroll
         for (int kt = 0; kt < KT_PER_CHUNK; ++kt) {
@@ -402,10 +426,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           uint32_t bfrag[MB][2];
 #pragma unroll
           for (int mb = 0; mb < MB; ++mb) {
-            const int row = mb * 8 + gid;
-            const uint32_t ra = st + L::OFF_A + row * 128 + t * 4;
-            bfrag[mb][0] = lds32(ra + (((kt * 2) ^ (row & 7)) << 4));
-            bfrag[mb][1] = lds32(ra + (((kt * 2 + 1) ^ (row & 7)) << 4));
+            const int sw = (mb * 8 + gid) & 7;
+            bfrag[mb][0] = *reinterpret_cast<const uint32_t*>(st + aoff[mb] + (((kt * 2) ^ sw) << 4));
+            bfrag[mb][1] = *reinterpret_cast<const uint32_t*>(st + aoff[mb] + (((kt * 2 + 1) ^ sw) << 4));
           }
           // scope bookkeeping (compile time after unrolling)
           constexpr int SC = (POST && SCOPE > 0) ? SCOPE : KT_PER_CHUNK;
@@ -416,13 +439,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           uint32_t sc[POST ? 1 : 8][2];
           if constexpr (!POST) {
             const int srow_local = (p.rpc == 1) ? 0 : (kt * 16) / p.group_size;
-            const uint32_t srow = st + L::OFF_S + srow_local * SROW_BYTES;
+            const uint32_t srow = smem_u32(st) + L::OFF_S + srow_local * SROW_BYTES;
 #pragma unroll
             for (int q = 0; q < 8; ++q) load_pre_scales<T, FMT>(srow, slot_col<BITS>(q, p_lane, gid), sc[q]);
           }
 
           // ---- weights ----
-          const uint32_t wb = st + kt * L::KT_BYTES + p_lane * 8;
+          const uint8_t* wb = st + kt * L::KT_BYTES;
           auto issue = [&](int q, const uint32_t (&a)[4]) {
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb) {
@@ -437,10 +460,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           if constexpr (BITS == 4) {
             uint2 x[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int lk = 2 * t + (i & 1) + ((i >> 1) << 3);
-              x[i] = lds64(wb + lk * 128 + ((gid ^ (lk & 7)) << 4));
-            }
+            for (int i = 0; i < 4; ++i) x[i] = *reinterpret_cast<const uint2*>(wb + woff[i]);
 #pragma unroll
             for (int s2 = 0; s2 < 2; ++s2) {
               const uint32_t x0 = s2 ? x[0].y : x[0].x, x1 = s2 ? x[1].y : x[1].x;
@@ -464,11 +484,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             for (int h = 0; h < 2; ++h) {
               uint2 x[4];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int lk = 2 * t + (i & 1) + ((i >> 1) << 3);
-                const int R = lk * 2 + h;
-                x[i] = lds64(wb + R * 128 + ((gid ^ (R & 7)) << 4));
-              }
+              for (int i = 0; i < 4; ++i) x[i] = *reinterpret_cast<const uint2*>(wb + woff[h * 4 + i]);
 #pragma unroll
               for (int s2 = 0; s2 < 2; ++s2) {
                 const uint32_t x0 = s2 ? x[0].y : x[0].x, x1 = s2 ? x[1].y : x[1].x;
@@ -501,10 +517,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             if constexpr (SCOPE > 0) {
               if (scope_last) {
                 const int srow_local = (p.rpc == 1) ? 0 : (kt * 16) / p.group_size;
-                const uint32_t srow = st + L::OFF_S + srow_local * SROW_BYTES;
-                const uint32_t zrow = st + L::OFF_Z + srow_local * SROW_BYTES;
-                auto ls = [&](int nb) { return lds32(srow + nb * 2); };
-                auto lz = [&](int nb) { return lds32(zrow + nb * 2); };
+                const uint8_t* srow = st + L::OFF_S + srow_local * SROW_BYTES;
+                const uint8_t* zrow = st + L::OFF_Z + srow_local * SROW_BYTES;
+                auto ls = [&](int nb) { return *reinterpret_cast<const uint32_t*>(srow + nb * 2); };
+                auto lz = [&](int nb) { return *reinterpret_cast<const uint32_t*>(zrow + nb * 2); };
                 fixup<T, FMT, MB, true>(acc, tmp, asum, ls, lz, p_lane, gid);
               }
             }
@@ -512,11 +528,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         }
       }  // alive
       __syncwarp();
-      if (lane == 0) mbar_arrive(empty_bar(s));
+      if (lane == 0) mbar_arrive(empty_bar(stage));
+      stage += PAIRS;
+      if (stage >= STAGES) { stage -= STAGES; phase ^= 1u; }
     }
 
-    // ---- end of a segment: add the partials of the four pairs, write out ----
-    if (u == u1 - 1 || c == p.kc - 1) {
+    // ---- end of the segment: add the partials of the four pairs, write out ----
+    {
       if constexpr (SCOPE == kWhole) {
         // per-channel scales: one fix-up for the whole segment, scales straight from global memory
         const uint32_t* sg = reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(p.scales) + (int64_t)g * GROUP_N);
@@ -551,7 +569,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 acc[q][mb][i] += v;
               }
         }
-        const bool full = (seg_first % p.kc == 0) && (c == p.kc - 1);
+        const bool full = (c0 == 0) && (seg_len == p.kc);
         if (full) {
           float alpha = 1.f;
           if constexpr (FMT == kNVFP4) alpha = p.global_scale[0];
@@ -577,7 +595,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             }
           }
         } else {
-          const int slot = (seg_first == u0) ? 0 : 1;
+          const int slot = first_segment ? 0 : 1;
           float* P = p.partials + ((int64_t)blockIdx.x * 2 + slot) * (MB * 8 * GROUP_N);
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
@@ -593,6 +611,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       }
       named_barrier_sync(1, CONSUMER_WARPS * 32);
     }
+    it0 += seg_len;
+    c0 = 0;
+    ++g;
+    first_segment = false;
   }
 }
 
@@ -726,9 +748,11 @@ int launch_one(const GemmArgs& g, const void* a, void* c, int m) {
   }
   decode_kernel<T, FMT, MB, SCOPE><<<p.num_ctas, THREADS, SMEM, g.stream>>>(tmW, tmA, tmS, tmZ, p);
   MB_CUDA(cudaGetLastError());
+  count_launches(1);
   if (U % p.num_ctas != 0 || (U / p.num_ctas) % p.kc != 0) {
     decode_reduce_kernel<T, FMT, MB><<<dim3(p.ng, m), GROUP_N, 0, g.stream>>>(p);
     MB_CUDA(cudaGetLastError());
+    count_launches(1);
   }
   return 0;
 }

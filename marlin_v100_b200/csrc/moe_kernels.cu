@@ -378,6 +378,7 @@ extern "C" int marlin_b200_moe_align_block_size(
                                                   sorted_token_ids, sorted_capacity, expert_ids,
                                                   expert_ids_capacity, num_tokens_post_pad);
     MB_CUDA(cudaGetLastError());
+    count_launches(1);
     return 0;
   }
   if (scratch_bytes < marlin_b200_moe_align_scratch_bytes(numel, num_experts) || scratch == nullptr) {
@@ -396,6 +397,7 @@ extern "C" int marlin_b200_moe_align_block_size(
                                                 (int)num_global_experts, expert_map, hist,
                                                 sorted_token_ids);
   MB_CUDA(cudaGetLastError());
+  count_launches(3);
   return 0;
 }
 
@@ -430,6 +432,7 @@ extern "C" int marlin_b200_topk_softmax(const void* gating, int gating_dtype, co
       MB_CHECK(false, "unsupported gating dtype %d", gating_dtype);
   }
   MB_CUDA(cudaGetLastError());
+  count_launches(1);
   return 0;
 }
 
@@ -446,6 +449,7 @@ extern "C" int marlin_b200_silu_and_mul(const void* in, void* out, int64_t rows,
     silu_and_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)in,
                                                             (__nv_bfloat16*)out, rows, inter);
   MB_CUDA(cudaGetLastError());
+  count_launches(1);
   return 0;
 }
 
@@ -462,5 +466,6 @@ extern "C" int marlin_b200_moe_sum(const void* in, void* out, int64_t tokens, in
     moe_sum_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out,
                                                        tokens, top_k, hidden);
   MB_CUDA(cudaGetLastError());
+  count_launches(1);
   return 0;
 }

@@ -85,6 +85,7 @@ extern "C" int marlin_b200_gptq_repack(const int32_t* b_q_weight, const int32_t*
     else gptq_repack_kernel<8, false><<<blocks, 256, 0, s>>>(in, perm, o, size_k, size_n, g);
   }
   MB_CUDA(cudaGetLastError());
+  count_launches(1);
   return 0;
 }
 
@@ -102,5 +103,6 @@ extern "C" int marlin_b200_awq_repack(const int32_t* b_q_weight, int32_t* out, i
   if (num_bits == 4) awq_repack_kernel<4><<<blocks, 256, 0, s>>>(in, o, size_k, size_n, g);
   else awq_repack_kernel<8><<<blocks, 256, 0, s>>>(in, o, size_k, size_n, g);
   MB_CUDA(cudaGetLastError());
+  count_launches(1);
   return 0;
 }
