@@ -51,7 +51,12 @@ struct StageLayout {
   static constexpr int OFF_S = OFF_A + A_BYTES;
   static constexpr int OFF_Z = OFF_S + META_BYTES;
   static constexpr int BYTES = OFF_Z + META_BYTES;  // multiple of 1024
-  static constexpr int STAGES = BITS == 4 ? 11 : 7;
+  // The ring depth is a multiple of PAIRS: a stage is then always consumed by the same pair.  With
+  // any other depth two pairs alternate on a stage, the later one can reach its wait a whole phase
+  // early, and an mbarrier parity wait cannot tell "one phase ahead" from "done" - it would read the
+  // stage too soon and release it twice.
+  static constexpr int STAGES = BITS == 4 ? 12 : 8;
+  static_assert(STAGES % PAIRS == 0, "a stage must belong to one pair");
 };
 
 // How the scales are applied.  kPre: multiply before the MMA (fp4).  Otherwise after the MMA, once
@@ -418,17 +423,32 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         atomicExch(&g_decode_status, 2);
         alive = false;
       }
-      const uint8_t* st = smem + stage * L::BYTES;
+      const uint32_t st = base + stage * L::BYTES;
+      const uint8_t* stp = smem + stage * L::BYTES;
       if (alive) {
+        // fragments of k-tile kt+1 are fetched while k-tile kt is being multiplied
+        constexpr int NW = (BITS == 4) ? 4 : 8;
+        uint2 xw[2][NW];
+        uint32_t bf[2][MB][2];
+        auto fetch = [&](int kt, int buf) {
 #pragma unroll
-        for (int kt = 0; kt < KT_PER_CHUNK; ++kt) {
-          // ---- activation fragments ----
-          uint32_t bfrag[MB][2];
+          for (int i = 0; i < NW; ++i) xw[buf][i] = *reinterpret_cast<const uint2*>(stp + kt * L::KT_BYTES + woff[i]);
 #pragma unroll
           for (int mb = 0; mb < MB; ++mb) {
             const int sw = (mb * 8 + gid) & 7;
-            bfrag[mb][0] = *reinterpret_cast<const uint32_t*>(st + aoff[mb] + (((kt * 2) ^ sw) << 4));
-            bfrag[mb][1] = *reinterpret_cast<const uint32_t*>(st + aoff[mb] + (((kt * 2 + 1) ^ sw) << 4));
+            bf[buf][mb][0] = *reinterpret_cast<const uint32_t*>(stp + aoff[mb] + (((kt * 2) ^ sw) << 4));
+            bf[buf][mb][1] = *reinterpret_cast<const uint32_t*>(stp + aoff[mb] + (((kt * 2 + 1) ^ sw) << 4));
+          }
+        };
+        fetch(0, 0);
+#pragma unroll
+        for (int kt = 0; kt < KT_PER_CHUNK; ++kt) {
+          if (kt + 1 < KT_PER_CHUNK) fetch(kt + 1, (kt + 1) & 1);
+          uint32_t bfrag[MB][2];
+#pragma unroll
+          for (int mb = 0; mb < MB; ++mb) {
+            bfrag[mb][0] = bf[kt & 1][mb][0];
+            bfrag[mb][1] = bf[kt & 1][mb][1];
           }
           // scope bookkeeping (compile time after unrolling)
           constexpr int SC = (POST && SCOPE > 0) ? SCOPE : KT_PER_CHUNK;
@@ -439,13 +459,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           uint32_t sc[POST ? 1 : 8][2];
           if constexpr (!POST) {
             const int srow_local = (p.rpc == 1) ? 0 : (kt * 16) / p.group_size;
-            const uint32_t srow = smem_u32(st) + L::OFF_S + srow_local * SROW_BYTES;
+            const uint32_t srow = st + L::OFF_S + srow_local * SROW_BYTES;
 #pragma unroll
             for (int q = 0; q < 8; ++q) load_pre_scales<T, FMT>(srow, slot_col<BITS>(q, p_lane, gid), sc[q]);
           }
 
           // ---- weights ----
-          const uint8_t* wb = st + kt * L::KT_BYTES;
           auto issue = [&](int q, const uint32_t (&a)[4]) {
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb) {
@@ -458,9 +477,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             }
           };
           if constexpr (BITS == 4) {
-            uint2 x[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) x[i] = *reinterpret_cast<const uint2*>(wb + woff[i]);
+            const uint2 (&x)[NW] = xw[kt & 1];
 #pragma unroll
             for (int s2 = 0; s2 < 2; ++s2) {
               const uint32_t x0 = s2 ? x[0].y : x[0].x, x1 = s2 ? x[1].y : x[1].x;
@@ -482,9 +499,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           } else {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-              uint2 x[4];
-#pragma unroll
-              for (int i = 0; i < 4; ++i) x[i] = *reinterpret_cast<const uint2*>(wb + woff[h * 4 + i]);
+              const uint2* x = &xw[kt & 1][h * 4];
 #pragma unroll
               for (int s2 = 0; s2 < 2; ++s2) {
                 const uint32_t x0 = s2 ? x[0].y : x[0].x, x1 = s2 ? x[1].y : x[1].x;
@@ -517,8 +532,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             if constexpr (SCOPE > 0) {
               if (scope_last) {
                 const int srow_local = (p.rpc == 1) ? 0 : (kt * 16) / p.group_size;
-                const uint8_t* srow = st + L::OFF_S + srow_local * SROW_BYTES;
-                const uint8_t* zrow = st + L::OFF_Z + srow_local * SROW_BYTES;
+                const uint8_t* srow = stp + L::OFF_S + srow_local * SROW_BYTES;
+                const uint8_t* zrow = stp + L::OFF_Z + srow_local * SROW_BYTES;
                 auto ls = [&](int nb) { return *reinterpret_cast<const uint32_t*>(srow + nb * 2); };
                 auto lz = [&](int nb) { return *reinterpret_cast<const uint32_t*>(zrow + nb * 2); };
                 fixup<T, FMT, MB, true>(acc, tmp, asum, ls, lz, p_lane, gid);
