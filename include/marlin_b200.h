@@ -101,6 +101,24 @@ int marlin_b200_gemm(const void* a, void* c, const int32_t* b_q_weight, const vo
                      int64_t a_stride, int64_t num_groups, void* scratch, int64_t scratch_bytes,
                      void* stream);
 
+/* Same computation as marlin_b200_gemm, for callers that cannot hand over a scratch buffer because
+ * they are not allowed to allocate device memory where the call happens (a serving runtime whose memory
+ * plan is fixed at start-up, a plugin that is given tensors but no allocator, host code that runs while
+ * another component captures the stream).  The split-K partial sums go to a 6 MiB array inside the
+ * library image instead (present on every GPU that loads the library, until the process exits), which
+ * covers devices of up to 192 SMs; a larger device gets MARLIN_B200_ESCRATCH and a message.  The call
+ * allocates nothing.  Its first use on a device resolves the array's device address: do that first
+ * call outside any stream capture.  All calls on a device share the array; nothing in it has to start
+ * at zero (every partial is written before it is read within one call), but two calls whose kernels
+ * overlap on the GPU (different streams) would overwrite each other's partial sums: keep calls to this
+ * entry point on one stream per device, or order them with events.
+ * This entry point has no counterpart in the reference. */
+int marlin_b200_gemm_static_scratch(const void* a, void* c, const int32_t* b_q_weight,
+                                    const void* b_scales, const void* b_zeros, const void* b_bias,
+                                    const float* global_scale, int act_dtype, int format,
+                                    int64_t size_m, int64_t size_n, int64_t size_k, int64_t a_stride,
+                                    int64_t num_groups, void* stream);
+
 /* ----------------------------------------------------------------------------------------------
  * Grouped expert GEMM.  Stands in for
  *   moe_wna16_marlin_gemm  csrc/moe/marlin_moe_wna16/ops.cu:102-529

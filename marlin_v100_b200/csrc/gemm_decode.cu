@@ -847,3 +847,54 @@ int launch_gemm_decode(const GemmArgs& g) {
 }
 
 }  // namespace mb200
+
+// ---------------------------------------------------------------------------------------------------
+// Dense GEMM with built-in scratch
+// ---------------------------------------------------------------------------------------------------
+namespace {
+// Room for the split-K partial sums of up to 192 SMs (two slots of 16 x 256 floats per SM).
+constexpr int64_t kStaticScratchBytes = 192ll * 2 * 16 * 256 * sizeof(float);  // 6 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+std::mutex g_static_mutex;
+void* g_static_ptr[64] = {};
+}  // namespace
+
+// marlin_b200_gemm for callers that must not allocate device memory around the call (a host runtime
+// with a fixed memory plan, a plugin that gets no allocator, code running between the capture calls
+// of someone else's stream): the split-K partial sums live in a 6 MiB array that is part of the
+// loaded library image on every GPU.  The first call on a device looks the array's device address
+// up (the name of the array is only a host-side handle, not an address a kernel could use); make
+// that first call before any stream capture starts on that device.
+extern "C" int marlin_b200_gemm_static_scratch(const void* a, void* c, const int32_t* b_q_weight,
+                                               const void* b_scales, const void* b_zeros, const void* b_bias,
+                                               const float* global_scale, int act_dtype, int format,
+                                               int64_t size_m, int64_t size_n, int64_t size_k, int64_t a_stride,
+                                               int64_t num_groups, void* stream) {
+  using namespace mb200;
+  int dev = 0;
+  MB_CUDA(cudaGetDevice(&dev));
+  MB_CHECK(dev >= 0 && dev < 64, "device ordinal %d is out of range for the built-in scratch table", dev);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        set_error("cudaGetSymbolAddress failed for the built-in scratch: %s", cudaGetErrorString(e));
+        return MARLIN_B200_ECUDA;
+      }
+      g_static_ptr[dev] = p;
+    }
+    scratch = g_static_ptr[dev];
+  }
+  const int64_t need = marlin_b200_gemm_scratch_bytes(size_m, size_n, size_k, format);
+  if (need > kStaticScratchBytes) {
+    set_error("this problem needs %lld bytes of scratch (%d SMs), the built-in scratch holds %lld: use "
+              "marlin_b200_gemm with a caller-provided buffer", (long long)need, sm_count(),
+              (long long)kStaticScratchBytes);
+    return MARLIN_B200_ESCRATCH;
+  }
+  return marlin_b200_gemm(a, c, b_q_weight, b_scales, b_zeros, b_bias, global_scale, act_dtype, format, size_m,
+                          size_n, size_k, a_stride, num_groups, scratch, kStaticScratchBytes, stream);
+}
