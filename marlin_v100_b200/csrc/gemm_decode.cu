@@ -37,9 +37,10 @@ namespace {
 constexpr int GROUP_N = 256;
 constexpr int KCHUNK = 64;
 constexpr int KT_PER_CHUNK = 4;
-constexpr int PAIRS = 4;
-constexpr int CONSUMER_WARPS = 2 * PAIRS;
-constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+// Four consumer pairs plus one producer warp.  (Five pairs were measured for the 4-bit formats: no
+// gain, the integer pipe that unpacks the codes is the shared limit.)
+__host__ __device__ constexpr int pairs_of(int bits) { return bits == 4 ? 4 : 4; }
+__host__ __device__ constexpr int threads_of(int bits) { return (2 * pairs_of(bits) + 1) * 32; }
 constexpr int META_BYTES = 2048;  // scale rows of one chunk: up to 4 rows x 512 B
 constexpr int A_BYTES = 2048;     // up to 16 token rows x 128 B
 
@@ -55,7 +56,8 @@ struct StageLayout {
   // any other depth two pairs alternate on a stage, the later one can reach its wait a whole phase
   // early, and an mbarrier parity wait cannot tell "one phase ahead" from "done" - it would read the
   // stage too soon and release it twice.
-  static constexpr int STAGES = BITS == 4 ? 12 : 8;
+  static constexpr int PAIRS = pairs_of(BITS);
+  static constexpr int STAGES = (BITS == 4 ? 3 : 2) * PAIRS;
   static_assert(STAGES % PAIRS == 0, "a stage must belong to one pair");
 };
 
@@ -291,13 +293,15 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 }
 
 template <typename T, int FMT, int MB, int SCOPE>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(threads_of(format_bits(FMT)), 1)
 decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
               const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
               const DecodeParams p) {
   constexpr int BITS = format_bits(FMT);
   using L = StageLayout<BITS>;
   constexpr int STAGES = L::STAGES;
+  constexpr int PAIRS = L::PAIRS;
+  constexpr int CONSUMER_WARPS = 2 * PAIRS;
   constexpr int ACC = 8 * MB * 4;  // floats per thread
   constexpr int RED_BYTES = (PAIRS - 1) * 2 * 32 * ACC * 4;
   constexpr bool POST = SCOPE != kPre;
@@ -331,16 +335,20 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const int64_t u1 = range_start(blockIdx.x + 1, U, p.num_ctas);
 
   if (warp == CONSUMER_WARPS) {
-    // ---------------- producer ----------------
-    if (lane == 0) {
+    // ---------------- producers ----------------
+    // Lane j feeds pair j: it owns the stages j, j + PAIRS, ... and every PAIRS-th chunk.  The lanes
+    // run the same loop side by side, which multiplies the rate at which chunks can be issued.
+    if (lane < PAIRS) {
       constexpr int ROWS_PER_KT = (BITS == 4) ? 16 : 32;  // 128-byte rows of one k-tile per group
-      int g = (int)(u0 / p.kc);
-      int c = (int)(u0 - (int64_t)g * p.kc);
       const int total = (int)(u1 - u0);
-      int s = 0;
+      int g = (int)(u0 / p.kc);
+      int c = (int)(u0 - (int64_t)g * p.kc) + lane;
+      while (c >= p.kc) { c -= p.kc; ++g; }
+      int s = lane;
       uint32_t phase = 0;
-      for (int it = 0; it < total; ++it) {
-        if (it >= STAGES) {
+      bool first_lap = true;
+      for (int it = lane; it < total; it += PAIRS) {
+        if (!first_lap) {
           if (!mbar_wait(empty_bar(s), phase ^ 1u, &s_abort)) {
             atomicExch(&g_decode_status, 1);
             break;
@@ -355,8 +363,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           tma_load_2d(st + L::OFF_S, &tmS, full_bar(s), g * GROUP_N, srow);
           if constexpr (format_has_zp(FMT)) tma_load_2d(st + L::OFF_Z, &tmZ, full_bar(s), g * GROUP_N, srow);
         }
-        if (++c == p.kc) { c = 0; ++g; }
-        if (++s == STAGES) { s = 0; phase ^= 1u; }
+        c += PAIRS;
+        while (c >= p.kc) { c -= p.kc; ++g; }
+        s += PAIRS;
+        if (s >= STAGES) { s -= STAGES; phase ^= 1u; first_lap = false; }
       }
     }
     return;
@@ -426,29 +436,18 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       const uint32_t st = base + stage * L::BYTES;
       const uint8_t* stp = smem + stage * L::BYTES;
       if (alive) {
-        // fragments of k-tile kt+1 are fetched while k-tile kt is being multiplied
         constexpr int NW = (BITS == 4) ? 4 : 8;
-        uint2 xw[2][NW];
-        uint32_t bf[2][MB][2];
-        auto fetch = [&](int kt, int buf) {
-#pragma unroll
-          for (int i = 0; i < NW; ++i) xw[buf][i] = *reinterpret_cast<const uint2*>(stp + kt * L::KT_BYTES + woff[i]);
-#pragma unroll
-          for (int mb = 0; mb < MB; ++mb) {
-            const int sw = (mb * 8 + gid) & 7;
-            bf[buf][mb][0] = *reinterpret_cast<const uint32_t*>(stp + aoff[mb] + (((kt * 2) ^ sw) << 4));
-            bf[buf][mb][1] = *reinterpret_cast<const uint32_t*>(stp + aoff[mb] + (((kt * 2 + 1) ^ sw) << 4));
-          }
-        };
-        fetch(0, 0);
 #pragma unroll
         for (int kt = 0; kt < KT_PER_CHUNK; ++kt) {
-          if (kt + 1 < KT_PER_CHUNK) fetch(kt + 1, (kt + 1) & 1);
+          uint2 xk[NW];
+#pragma unroll
+          for (int i = 0; i < NW; ++i) xk[i] = *reinterpret_cast<const uint2*>(stp + kt * L::KT_BYTES + woff[i]);
           uint32_t bfrag[MB][2];
 #pragma unroll
           for (int mb = 0; mb < MB; ++mb) {
-            bfrag[mb][0] = bf[kt & 1][mb][0];
-            bfrag[mb][1] = bf[kt & 1][mb][1];
+            const int sw = (mb * 8 + gid) & 7;
+            bfrag[mb][0] = *reinterpret_cast<const uint32_t*>(stp + aoff[mb] + (((kt * 2) ^ sw) << 4));
+            bfrag[mb][1] = *reinterpret_cast<const uint32_t*>(stp + aoff[mb] + (((kt * 2 + 1) ^ sw) << 4));
           }
           // scope bookkeeping (compile time after unrolling)
           constexpr int SC = (POST && SCOPE > 0) ? SCOPE : KT_PER_CHUNK;
@@ -477,7 +476,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             }
           };
           if constexpr (BITS == 4) {
-            const uint2 (&x)[NW] = xw[kt & 1];
+            const uint2 (&x)[NW] = xk;
 #pragma unroll
             for (int s2 = 0; s2 < 2; ++s2) {
               const uint32_t x0 = s2 ? x[0].y : x[0].x, x1 = s2 ? x[1].y : x[1].x;
@@ -499,7 +498,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           } else {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-              const uint2* x = &xw[kt & 1][h * 4];
+              const uint2* x = &xk[h * 4];
 #pragma unroll
               for (int s2 = 0; s2 < 2; ++s2) {
                 const uint32_t x0 = s2 ? x[0].y : x[0].x, x1 = s2 ? x[1].y : x[1].x;
@@ -700,6 +699,8 @@ int launch_one(const GemmArgs& g, const void* a, void* c, int m) {
   constexpr int BITS = format_bits(FMT);
   using L = StageLayout<BITS>;
   constexpr int ACC = 8 * MB * 4;
+  constexpr int PAIRS = L::PAIRS;
+  constexpr int THREADS = threads_of(BITS);
   constexpr int SMEM = 1024 + L::STAGES * L::BYTES + (PAIRS - 1) * 2 * 32 * ACC * 4 + 2 * L::STAGES * 8;
   static_assert(SMEM <= 227 * 1024, "shared memory budget");
 
