@@ -99,8 +99,14 @@ int dispatch(const GemmArgs& g) {
     set_error("size_k must be positive");
     return MARLIN_B200_EINVAL;
   }
+  // M <= 16: weight-streaming kernel.  Larger M: tensor-memory kernel; shapes it does not take fall
+  // back to passes of the streaming kernel, and anything else to the shape-agnostic kernel.
+  if (g.size_m > 16) {
+    const int rc = launch_gemm_tc(g);
+    if (rc <= 0) return rc;  // handled (0) or failed (<0)
+  }
   const int rc = launch_gemm_decode(g);
-  if (rc <= 0) return rc;  // handled (0) or failed (<0)
+  if (rc <= 0) return rc;
   return launch_gemm_generic(g);
 }
 

@@ -1,0 +1,599 @@
+// Tensor-memory GEMM for M > 16: C[M, N] = A[M, K] * dequant(B)[K, N] on the 5th-generation tensor
+// cores (tcgen05.mma, accumulators in TMEM).
+//
+// One persistent CTA per SM, 512 threads, warp-specialised:
+//   warp 0      TMA producer of the packed weight chunks (+ their scale / zero-point rows)
+//   warp 1      TMA producer of the activation tiles
+//   warp 2      allocates tensor memory, issues the MMAs (one thread)
+//   warps 4-7   epilogue: tcgen05.ld the accumulator, bias / nvfp4 global scale, store C
+//   warps 8-15  dequantise: packed codes (shared memory) -> K-major 128-byte-swizzled operand tile
+//               of the activation type, scaled per group, in shared memory
+// Output tile: (128 * MT) rows x 256 columns (one packed column group), K walked in chunks of 64.
+// Per chunk the tensor core runs 4 * MT MMAs of 128 x 256 x 16; the two 128-row halves share the
+// dequantised weight tile, which halves the dequantisation work and the operand-write traffic per
+// flop (MT = 2).  The accumulators use 256 * MT of the 512 TMEM columns.
+//
+// Pipelines (all mbarrier based, every wait bounded):
+//   raw ring   : TMA -> dequant warps                (raw_full / raw_empty)
+//   A ring     : TMA -> MMA                          (a_full / a_empty via tcgen05.commit)
+//   B ring     : dequant warps -> MMA                (b_full / b_empty via tcgen05.commit)
+//   accumulator: MMA -> epilogue -> MMA              (acc_full via tcgen05.commit / acc_empty)
+#include <mutex>
+#include <unordered_map>
+
+#include "codes.cuh"
+#include "common.cuh"
+#include "tma.cuh"
+
+namespace mb200 {
+namespace {
+
+using namespace codes;
+
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int KT = 4;            // k-tiles of 16 per chunk
+constexpr int META = 2048;       // bytes reserved for the scale rows of a chunk (and again for zeros)
+constexpr int THREADS = 512;
+constexpr int DQ_WARPS = 8;
+
+template <int BITS, int MT>
+struct TcLayout {
+  static constexpr int RAW_W = KT * 16 * BN * BITS / 8;  // 8 KiB / 16 KiB
+  static constexpr int RAW_BYTES = RAW_W + 2 * META;
+  static constexpr int RAW_STAGES = BITS == 4 ? 3 : 2;
+  static constexpr int A_BYTES = MT * 128 * 128;
+  static constexpr int A_STAGES = 3;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int B_STAGES = 2;
+  static constexpr int OFF_RAW = 0;
+  static constexpr int OFF_A = OFF_RAW + RAW_STAGES * RAW_BYTES;
+  static constexpr int OFF_B = OFF_A + A_STAGES * A_BYTES;
+  static constexpr int OFF_BAR = OFF_B + B_STAGES * B_BYTES;
+  static constexpr int NUM_BARS = 2 * RAW_STAGES + 2 * A_STAGES + 2 * B_STAGES + 2;
+  static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16;
+};
+
+struct TcParams {
+  void* c;
+  const void* bias;
+  const float* global_scale;
+  int M, N, K;
+  int num_groups, group_size, rpc;
+  int kc;       // chunks along K
+  int m_tiles, n_tiles;
+  uint32_t raw_tx, a_tx;
+};
+
+__device__ int g_tc_status = 0;
+
+// ---- tcgen05 wrappers -----------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle:
+// 8-row groups are 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;               // leading byte offset (unused for this layout), 16 B
+  d |= (uint64_t)(1024 >> 4) << 32;     // stride byte offset
+  d |= (uint64_t)1 << 46;               // version
+  d |= (uint64_t)2 << 61;               // SWIZZLE_128B
+  return d;
+}
+
+// kind::f16 instruction descriptor: fp32 accumulate, A and B both T, both K-major, M = 128, N = 256.
+template <typename T>
+__device__ __forceinline__ constexpr uint32_t instr_desc() {
+  uint32_t d = 0;
+  d |= 1u << 4;                                  // D format f32
+  d |= (kHalf<T> ? 0u : 1u) << 7;                // A format
+  d |= (kHalf<T> ? 0u : 1u) << 10;               // B format
+  d |= (uint32_t)(BN >> 3) << 17;                // N
+  d |= (uint32_t)(128 >> 4) << 24;               // M
+  return d;
+}
+
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// ---- dequantisation of one chunk (256 columns x 64 k) by the eight dequant warps ------------------------
+// Warp d handles the 8 k of 16-byte chunk index d of every row (k-tile d >> 1, half d & 1); lane ->
+// (64-column tile sub = lane >> 3, 8-column vector nv = lane & 7).  The thread reads the 8 (16) packed
+// words of its columns (conflict-free: the 32 lanes read one 128-byte line), pairs consecutive k with
+// byte permutes, decodes, applies scale / zero and writes, per column, the 16 bytes (8 k) of the
+// operand row at its swizzled position.
+//
+// Store order: in step s a lane does not write its column s but column s ^ nv (4-bit) resp.
+// s ^ (nv >> 1) (8-bit).  The eight lanes of a quarter warp then hit eight different rows mod 8,
+// i.e. eight different 16-byte positions of the swizzled 128-byte lines, and the 16-byte stores
+// are bank-conflict free.  The column index is a run-time value, so codes are picked with run-time
+// shifts / permute selectors and the scale of the column is fetched from shared memory.
+template <typename T>
+__device__ __forceinline__ uint32_t scale_pair_at(uint32_t row, int n) {
+  const uint32_t w = lds16(row + n * 2);
+  return prmt(w, w, 0x1010u);
+}
+
+template <typename T, int FMT>
+__device__ __forceinline__ void dequant_chunk(uint32_t raw, uint32_t btile, int d, int lane, int rpc, int group_size) {
+  constexpr int BITS = format_bits(FMT);
+  constexpr int RAW_W = KT * 16 * BN * BITS / 8;
+  constexpr int SROW = format_scale_is_byte(FMT) ? BN : BN * 2;
+  const int kt = d >> 1, half = d & 1;
+  const int sub = lane >> 3, nv = lane & 7;
+  const int row_local = (rpc == 1) ? 0 : (kt * 16 + half * 8) / group_size;
+  const uint32_t srow = raw + RAW_W + row_local * SROW;
+  const uint32_t zrow = raw + RAW_W + META + row_local * SROW;
+
+  if constexpr (BITS == 4) {
+    const int n8 = sub * 64 + nv * 8;
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int lk = half * 8 + i;
+      w[i] = lds32(raw + kt * 2048 + lk * 128 + ((nv ^ (lk & 7)) << 4) + sub * 4);
+    }
+    // za: codes of the columns whose parity equals this lane's nv parity ... zb: the other parity.
+    // (low 16 bits of a word = even columns 0,2,4,6; high 16 bits = odd columns 1,3,5,7)
+    const uint32_t sel_a = (nv & 1) ? 0x7632u : 0x5410u, sel_b = (nv & 1) ? 0x5410u : 0x7632u;
+    uint32_t za[4], zb[4];
+#pragma unroll
+    for (int kp = 0; kp < 4; ++kp) {
+      za[kp] = prmt(w[2 * kp], w[2 * kp + 1], sel_a);
+      zb[kp] = prmt(w[2 * kp], w[2 * kp + 1], sel_b);
+    }
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      const int j = s ^ nv;                 // column handled in this step
+      const int m = j >> 1;                 // its code index inside the 16-bit half
+      const int n = n8 + j;
+      uint32_t sp, zp = 0;
+      if constexpr (FMT == kNVFP4) {
+        const int pos = (j & 4) + ((j & 3) == 1 ? 2 : (j & 3) == 2 ? 1 : (j & 3));
+        sp = fp4_scale_pair<T, FMT>(lds16(srow + ((n8 + pos) & ~1)) >> (8 * (pos & 1)) & 0xffu);
+      } else if constexpr (FMT == kMXFP4) {
+        sp = fp4_scale_pair<T, FMT>((lds16(srow + (n & ~1)) >> (8 * (n & 1))) & 0xffu);
+      } else {
+        sp = scale_pair_at<T>(srow, n);
+        if constexpr (format_has_zp(FMT)) zp = scale_pair_at<T>(zrow, n) ^ 0x80008000u;
+      }
+      uint32_t v[4];
+#pragma unroll
+      for (int kp = 0; kp < 4; ++kp) {
+        const uint32_t z = (s & 1) ? zb[kp] : za[kp];
+        uint32_t q;
+        if constexpr (FMT == kU4B8 || FMT == kU4) {
+          constexpr uint32_t zero = (FMT == kU4B8) ? 8 : 0;
+          constexpr uint32_t magic = kHalf<T> ? 0x6400u : 0x4300u;  // 1024 / 128: one unit per code step
+          constexpr uint32_t c = magic + zero;
+          q = psub<T>(((z >> (4 * m)) & 0x000f000fu) | (magic | (magic << 16)), c | (c << 16));
+        } else {
+          const uint32_t t = z << (12 - 4 * m);
+          constexpr int sh = kHalf<T> ? 3 : 6;
+          q = ((t & 0x70007000u) >> sh) | (t & 0x80008000u);
+        }
+        if constexpr (format_has_zp(FMT)) v[kp] = pfma<T>(q, sp, zp);
+        else v[kp] = pmul<T>(q, sp);
+      }
+      sts128(btile + n * 128 + ((d ^ j) << 4), v[0], v[1], v[2], v[3]);
+    }
+  } else {
+    const int rot = (nv >> 1) & 3;
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int n4 = sub * 64 + (nv + 8 * hh) * 4;
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int R = (half * 8 + i) * 2 + hh;
+        w[i] = lds32(raw + kt * 4096 + R * 128 + ((nv ^ (R & 7)) << 4) + sub * 4);
+      }
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const int j = s ^ rot;                         // column handled in this step
+        const int bp = (j & 1) * 2 + (j >> 1);         // its byte inside the word
+        const uint32_t sel = (uint32_t)bp | ((uint32_t)(4 + bp) << 4);
+        const int n = n4 + j;
+        const uint32_t sp = scale_pair_at<T>(srow, n);
+        uint32_t zp = 0;
+        if constexpr (format_has_zp(FMT)) zp = scale_pair_at<T>(zrow, n) ^ 0x80008000u;
+        uint32_t v[4];
+#pragma unroll
+        for (int kp = 0; kp < 4; ++kp) {
+          const uint32_t y = prmt(w[2 * kp], w[2 * kp + 1], sel);  // bytes 0,1 = the code at k0, k1
+          const uint32_t q = value8<T, FMT>(y, 0);
+          if constexpr (format_has_zp(FMT)) v[kp] = pfma<T>(q, sp, zp);
+          else v[kp] = pmul<T>(q, sp);
+        }
+        sts128(btile + n * 128 + ((d ^ (n & 7)) << 4), v[0], v[1], v[2], v[3]);
+      }
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack_out(float a, float b) {
+  if constexpr (kHalf<T>) {
+    __half2 r = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&r);
+  } else {
+    __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+}
+
+template <typename T, int FMT, int MT>
+__global__ void __launch_bounds__(THREADS, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
+               const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ, const TcParams p) {
+  constexpr int BITS = format_bits(FMT);
+  using L = TcLayout<BITS, MT>;
+  constexpr int RS = L::RAW_STAGES, AS = L::A_STAGES, BS = L::B_STAGES;
+  constexpr uint32_t NCOLS = 256 * MT;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar0 = base + L::OFF_BAR;
+  auto raw_full = [&](int s) { return bar0 + 8u * s; };
+  auto raw_empty = [&](int s) { return bar0 + 8u * (RS + s); };
+  auto a_full = [&](int s) { return bar0 + 8u * (2 * RS + s); };
+  auto a_empty = [&](int s) { return bar0 + 8u * (2 * RS + AS + s); };
+  auto b_full = [&](int s) { return bar0 + 8u * (2 * RS + 2 * AS + s); };
+  auto b_empty = [&](int s) { return bar0 + 8u * (2 * RS + 2 * AS + BS + s); };
+  const uint32_t acc_full = bar0 + 8u * (2 * RS + 2 * AS + 2 * BS);
+  const uint32_t acc_empty = acc_full + 8u;
+  const uint32_t tmem_slot = acc_empty + 8u;
+
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    s_abort = 0;
+    for (int s = 0; s < RS; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DQ_WARPS); }
+    for (int s = 0; s < AS; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
+    for (int s = 0; s < BS; ++s) { mbar_init(b_full(s), DQ_WARPS); mbar_init(b_empty(s), 1); }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 4);
+    fence_barrier_init();
+    prefetch_tensormap(&tmW);
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmS);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, NCOLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  const int num_tiles = p.m_tiles * p.n_tiles;
+  constexpr int ROWS_PER_KT = (BITS == 4) ? 16 : 32;
+
+  if (warp == 0) {
+    // ---------------- packed-weight producer ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int nt = tile / p.m_tiles;
+        for (int c = 0; c < p.kc; ++c) {
+          if (!mbar_wait(raw_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 1); ok = false; break; }
+          const uint32_t st = base + L::OFF_RAW + s * L::RAW_BYTES;
+          mbar_arrive_expect_tx(raw_full(s), p.raw_tx);
+          tma_load_3d(st, &tmW, raw_full(s), 0, nt * ROWS_PER_KT, c * KT);
+          const int srow = (p.num_groups == 1) ? 0 : (c * BK) / p.group_size;
+          tma_load_2d(st + L::RAW_W, &tmS, raw_full(s), nt * BN, srow);
+          if constexpr (format_has_zp(FMT)) tma_load_2d(st + L::RAW_W + META, &tmZ, raw_full(s), nt * BN, srow);
+          if (++s == RS) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- activation producer ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int mt = tile % p.m_tiles;
+        for (int c = 0; c < p.kc; ++c) {
+          if (!mbar_wait(a_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 2); ok = false; break; }
+          mbar_arrive_expect_tx(a_full(s), p.a_tx);
+          tma_load_2d(base + L::OFF_A + s * L::A_BYTES, &tmA, a_full(s), c * BK, mt * 128 * MT);
+          if (++s == AS) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc<T>();
+      int sa = 0, sb = 0;
+      uint32_t pha = 0, phb = 0, phacc = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(acc_empty, phacc ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 3); ok = false; break; }
+        tc_fence_after();
+        for (int c = 0; c < p.kc; ++c) {
+          if (!mbar_wait(a_full(sa), pha, &s_abort) || !mbar_wait(b_full(sb), phb, &s_abort)) {
+            atomicExch(&g_tc_status, 4);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = base + L::OFF_A + sa * L::A_BYTES;
+          const uint32_t b_addr = base + L::OFF_B + sb * L::B_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t bdesc = kmajor_sw128_desc(b_addr + kk * 32);
+#pragma unroll
+            for (int h = 0; h < MT; ++h) {
+              const uint64_t adesc = kmajor_sw128_desc(a_addr + h * (128 * 128) + kk * 32);
+              tc_mma_f16(tmem_base + h * 256, adesc, bdesc, idesc, (c > 0 || kk > 0) ? 1u : 0u);
+            }
+          }
+          tc_commit(a_empty(sa));
+          tc_commit(b_empty(sb));
+          if (++sa == AS) { sa = 0; pha ^= 1u; }
+          if (++sb == BS) { sb = 0; phb ^= 1u; }
+        }
+        if (ok) tc_commit(acc_full);
+        phacc ^= 1u;
+      }
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ---------------- epilogue ----------------
+    const int q = warp - 4;
+    uint32_t ph = 0;
+    float alpha = 1.f;
+    if constexpr (FMT == kNVFP4) alpha = p.global_scale[0];
+    T* C = reinterpret_cast<T*>(p.c);
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+      if (!mbar_wait(acc_full, ph, &s_abort)) { atomicExch(&g_tc_status, 5); break; }
+      ph ^= 1u;
+      tc_fence_after();
+#pragma unroll 1
+      for (int h = 0; h < MT; ++h) {
+        const int row = mt * 128 * MT + h * 128 + q * 32 + lane;
+#pragma unroll 1
+        for (int cb = 0; cb < BN / 32; ++cb) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + h * 256 + cb * 32, v);
+          tmem_ld_wait();
+          const int col0 = nt * BN + cb * 32;
+          if (row < p.M) {
+            uint32_t o[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float x0 = __uint_as_float(v[2 * i]) * alpha, x1 = __uint_as_float(v[2 * i + 1]) * alpha;
+              if (bias != nullptr) {
+                x0 += to_float<T>(bias[bias_index(col0 + 2 * i)]);
+                x1 += to_float<T>(bias[bias_index(col0 + 2 * i + 1)]);
+              }
+              o[i] = pack_out<T>(x0, x1);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(C + (int64_t)row * p.N + col0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty);
+    }
+  } else if (warp >= 8) {
+    // ---------------- dequantisation ----------------
+    const int d = warp - 8;
+    int sr = 0, sb = 0;
+    uint32_t phr = 0, phb = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int c = 0; c < p.kc; ++c) {
+        if (!mbar_wait(raw_full(sr), phr, &s_abort) || !mbar_wait(b_empty(sb), phb ^ 1u, &s_abort)) {
+          atomicExch(&g_tc_status, 6);
+          ok = false;
+          break;
+        }
+        dequant_chunk<T, FMT>(base + L::OFF_RAW + sr * L::RAW_BYTES, base + L::OFF_B + sb * L::B_BYTES, d, lane,
+                              p.rpc, p.group_size);
+        fence_proxy_async();  // the tensor core reads the tile through the async proxy
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(b_full(sb));
+          mbar_arrive(raw_empty(sr));
+        }
+        if (++sr == RS) { sr = 0; phr ^= 1u; }
+        if (++sb == BS) { sb = 0; phb ^= 1u; }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, NCOLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------
+struct MapKey {
+  const void* ptr;
+  int64_t a, b, c;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && a == o.a && b == o.b && c == o.c; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.ptr) ^ (std::hash<int64_t>()(k.a) * 31) ^ (std::hash<int64_t>()(k.b) * 131) ^
+           (std::hash<int64_t>()(k.c) * 977);
+  }
+};
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+
+int cached_map(CUtensorMap* out, const MapKey& key, CUtensorMapDataType dt, int rank, const void* base,
+               const uint64_t* dims, const uint64_t* strides, const uint32_t* box, CUtensorMapSwizzle sw) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  auto it = g_map_cache.find(key);
+  if (it != g_map_cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  if (int rc = encode_tensor_map(out, dt, rank, base, dims, strides, box, sw)) return rc;
+  if (g_map_cache.size() > 4096) g_map_cache.clear();
+  g_map_cache.emplace(key, *out);
+  return 0;
+}
+
+template <typename T, int FMT, int MT>
+int launch_tc(const GemmArgs& g) {
+  constexpr int BITS = format_bits(FMT);
+  using L = TcLayout<BITS, MT>;
+  constexpr int SMEM = 1024 + L::TOTAL;
+  static_assert(SMEM <= 227 * 1024, "shared memory budget");
+  const int64_t K = g.size_k, N = g.size_n, M = g.size_m;
+  const int64_t gs = K / g.num_groups;
+  TcParams p{};
+  p.c = g.c; p.bias = g.bias; p.global_scale = g.global_scale;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.num_groups = (int)g.num_groups; p.group_size = (int)gs;
+  p.rpc = (g.num_groups > 1 && gs < BK) ? (int)(BK / gs) : 1;
+  p.kc = (int)((K + BK - 1) / BK);
+  p.m_tiles = (int)((M + 128 * MT - 1) / (128 * MT));
+  p.n_tiles = (int)(N / BN);
+  const int srow_bytes = format_scale_is_byte(FMT) ? BN : BN * 2;
+  p.raw_tx = L::RAW_W + p.rpc * srow_bytes * (format_has_zp(FMT) ? 2 : 1);
+  p.a_tx = L::A_BYTES;
+
+  CUtensorMap tmW, tmA, tmS, tmZ;
+  {
+    const int rows_per_kt = (BITS == 4 ? 16 : 32) * p.n_tiles;
+    const uint64_t dims[3] = {32, (uint64_t)rows_per_kt, (uint64_t)(K / 16)};
+    const uint64_t strides[2] = {128, (uint64_t)rows_per_kt * 128};
+    const uint32_t box[3] = {32, (uint32_t)(BITS == 4 ? 16 : 32), KT};
+    if (int rc = cached_map(&tmW, MapKey{g.bq, N, K, BITS}, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.bq, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t strides[1] = {(uint64_t)g.a_stride * 2};
+    const uint32_t box[2] = {BK, 128 * MT};
+    if (int rc = encode_tensor_map(&tmA, kHalf<T> ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                   g.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  {
+    const bool byte_scale = format_scale_is_byte(FMT);
+    const uint64_t dims[2] = {(uint64_t)N, (uint64_t)g.num_groups};
+    const uint64_t strides[1] = {(uint64_t)N * (byte_scale ? 1 : 2)};
+    const uint32_t box[2] = {BN, (uint32_t)p.rpc};
+    const CUtensorMapDataType dt = byte_scale ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+    if (int rc = cached_map(&tmS, MapKey{g.scales, N, g.num_groups, p.rpc * 16 + byte_scale}, dt, 2, g.scales, dims,
+                            strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+      return rc;
+    tmZ = tmS;
+    if (format_has_zp(FMT)) {
+      if (int rc = cached_map(&tmZ, MapKey{g.zeros, N, g.num_groups, p.rpc * 16 + byte_scale}, dt, 2, g.zeros, dims,
+                              strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return rc;
+    }
+  }
+  static bool attr_set[64] = {};
+  int dev = 0;
+  MB_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    MB_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<T, FMT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    attr_set[dev] = true;
+  }
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  tc_gemm_kernel<T, FMT, MT><<<grid, THREADS, SMEM, g.stream>>>(tmW, tmA, tmS, tmZ, p);
+  MB_CUDA(cudaGetLastError());
+  count_launches(1);
+  return 0;
+}
+
+template <typename T, int FMT>
+int launch_fmt(const GemmArgs& g) {
+  if (g.size_m <= 128) return launch_tc<T, FMT, 1>(g);
+  return launch_tc<T, FMT, 2>(g);
+}
+
+template <typename T>
+int launch_dtype(const GemmArgs& g) {
+  switch (g.format) {
+    case kU4B8: return launch_fmt<T, kU4B8>(g);
+    case kU4: return launch_fmt<T, kU4>(g);
+    case kU8B128: return launch_fmt<T, kU8B128>(g);
+    case kU8: return launch_fmt<T, kU8>(g);
+    case kFP8: return launch_fmt<T, kFP8>(g);
+    case kNVFP4: return launch_fmt<T, kNVFP4>(g);
+    case kMXFP4: return launch_fmt<T, kMXFP4>(g);
+  }
+  return 1;
+}
+
+}  // namespace
+
+// Returns 1 when the problem is not one this kernel takes.
+int launch_gemm_tc(const GemmArgs& g) {
+  if (g.sorted_ids != nullptr) return 1;
+  if (g.size_m <= 0 || g.size_n % BN != 0 || g.size_k % 32 != 0) return 1;
+  if (g.num_groups > 1) {
+    const int64_t gs = g.size_k / g.num_groups;
+    if (!(gs == 16 || gs == 32 || gs % BK == 0)) return 1;
+  }
+  if (g.act_dtype == MARLIN_B200_F16) return launch_dtype<__half>(g);
+  return launch_dtype<__nv_bfloat16>(g);
+}
+
+}  // namespace mb200
