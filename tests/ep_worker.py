@@ -1,0 +1,54 @@
+"""Worker of the multi-GPU expert-parallel check: launched with torchrun, one rank per GPU.
+Every rank builds the same seeded layer on the CPU, keeps its expert shard and its token shard,
+runs the expert-parallel layer (NCCL all-to-all dispatch / combine around the local fused expert
+layer) and compares its tokens with the CPU oracle of the whole layer."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from oracle import marlin_oracle as mo  # noqa: E402
+from tests import util  # noqa: E402
+from marlin_v100_b200 import fused_moe, parallel  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    fmt, dtype = "mxfp4", torch.bfloat16
+    e, k, hdim, inter, tokens = 8 * world, 4, 256, 128, 32 * world
+    g = torch.Generator().manual_seed(5)
+    hidden = torch.randn(tokens, hdim, generator=g).to(dtype)
+    logits = torch.randn(tokens, e, generator=g)
+    w13 = util.make_experts(e, hdim, 2 * inter, fmt, dtype, seed=6, scale=0.05)
+    w2 = util.make_experts(e, inter, hdim, fmt, dtype, seed=7, scale=0.05)
+    per = e // world
+    sl_e = slice(rank * per, (rank + 1) * per)
+    tok = tokens // world
+    sl_t = slice(rank * tok, (rank + 1) * tok)
+    dev = "cuda"
+    layer = parallel.ExpertParallelMoE.from_marlin_weights(
+        w13.packed[sl_e].to(dev), w2.packed[sl_e].to(dev), w13.scales[sl_e].to(dev), w2.scales[sl_e].to(dev),
+        w13.type_id, e)
+    tw, ids, _ = fused_moe.fused_topk(logits[sl_t].to(dev), k, True)
+    out = layer.forward(hidden[sl_t].to(dev), tw, ids)
+    torch.cuda.synchronize()
+    rtw, rids, _ = mo.topk_softmax_reference(logits, k, True)
+    ref = mo.moe_reference(hidden, w13.deq, w2.deq, rtw, rids, round_dtype=dtype)[sl_t]
+    ok = torch.equal(ids.cpu(), rids[sl_t]) and mo.within_tolerance(out.cpu(), ref)
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("EP_OK" if int(flag) == 1 else f"EP_FAIL mean_rel={mo.mean_rel_err(out.cpu(), ref):.3e}", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,43 @@
+"""Expert-parallel layer on GPUs: world size 1 must equal the plain fused layer; with two or more
+GPUs a torchrun job checks the NCCL dispatch / combine against the CPU oracle."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from oracle import marlin_oracle as mo
+from tests import util
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_world1_equals_fused_layer():
+    from marlin_v100_b200 import fused_moe, parallel
+    e, k, hdim, inter, t = 8, 2, 256, 128, 40
+    g = torch.Generator().manual_seed(2)
+    hidden = torch.randn(t, hdim, generator=g).to(torch.float16)
+    logits = torch.randn(t, e, generator=g)
+    w13 = util.make_experts(e, hdim, 2 * inter, "u4b8", torch.float16, seed=3, scale=0.05)
+    w2 = util.make_experts(e, inter, hdim, "u4b8", torch.float16, seed=4, scale=0.05)
+    d13, d2 = util.to_dev(w13), util.to_dev(w2)
+    tw, ids, _ = fused_moe.fused_topk(logits.cuda(), k, True)
+    layer = parallel.ExpertParallelMoE.from_marlin_weights(d13.packed, d2.packed, d13.scales, d2.scales,
+                                                           w13.type_id, e)
+    out = layer.forward(hidden.cuda(), tw, ids)
+    rtw, rids, _ = mo.topk_softmax_reference(logits, k, True)
+    ref = mo.moe_reference(hidden, w13.deq, w2.deq, rtw, rids, round_dtype=torch.float16)
+    assert mo.within_tolerance(out.cpu(), ref)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_multi_gpu_dispatch_combine():
+    n = min(torch.cuda.device_count(), 4)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29541",
+                        os.path.join(ROOT, "tests", "ep_worker.py")], capture_output=True, text=True, env=env,
+                       timeout=600)
+    assert r.returncode == 0 and "EP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
