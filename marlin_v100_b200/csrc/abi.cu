@@ -187,5 +187,7 @@ extern "C" int marlin_b200_moe_gemm(const void* a, void* c, const int32_t* b_q_w
   MB_CHECK(!mul_topk_weights || topk_weights != nullptr, "mul_topk_weights needs topk_weights");
   MB_CHECK(size_m * top_k < (1ll << 31), "size_m * top_k does not fit 32-bit route ids");
   if (g.size_m == 0 || g.size_n == 0 || num_sorted == 0) return 0;
+  const int rc = launch_gemm_tc(g);  // tensor-memory grouped kernel when the shape qualifies
+  if (rc <= 0) return rc;
   return launch_gemm_generic(g);
 }

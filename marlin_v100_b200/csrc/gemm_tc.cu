@@ -1,12 +1,12 @@
 // Tensor-memory GEMM for M > 16: C[M, N] = A[M, K] * dequant(B)[K, N] on the 5th-generation tensor
 // cores (tcgen05.mma, accumulators in TMEM).
 //
-// One persistent CTA per SM, 512 threads, warp-specialised:
+// One persistent CTA per SM, 768 threads, warp-specialised:
 //   warp 0      TMA producer of the packed weight chunks (+ their scale / zero-point rows)
 //   warp 1      TMA producer of the activation tiles
 //   warp 2      allocates tensor memory, issues the MMAs (one thread)
 //   warps 4-7   epilogue: tcgen05.ld the accumulator, bias / nvfp4 global scale, store C
-//   warps 8-15  dequantise: packed codes (shared memory) -> K-major 128-byte-swizzled operand tile
+//   warps 8-23  dequantise: packed codes (shared memory) -> K-major 128-byte-swizzled operand tile
 //               of the activation type, scaled per group, in shared memory
 // Output tile: (128 * MT) rows x 256 columns (one packed column group), K walked in chunks of 64.
 // Per chunk the tensor core runs 4 * MT MMAs of 128 x 256 x 16; the two 128-row halves share the
@@ -34,16 +34,17 @@ constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int KT = 4;            // k-tiles of 16 per chunk
 constexpr int META = 2048;       // bytes reserved for the scale rows of a chunk (and again for zeros)
-constexpr int THREADS = 512;
-constexpr int DQ_WARPS = 8;
+constexpr int THREADS = 768;
+constexpr int DQ_WARPS = 16;
+constexpr int MOE_A_STAGES = 6;  // the gathered activation ring is deeper: gathers have a long latency
 
-template <int BITS, int MT>
+template <int BITS, int MT, int AST = 3>
 struct TcLayout {
   static constexpr int RAW_W = KT * 16 * BN * BITS / 8;  // 8 KiB / 16 KiB
   static constexpr int RAW_BYTES = RAW_W + 2 * META;
   static constexpr int RAW_STAGES = BITS == 4 ? 3 : 2;
   static constexpr int A_BYTES = MT * 128 * 128;
-  static constexpr int A_STAGES = 3;
+  static constexpr int A_STAGES = AST;
   static constexpr int B_BYTES = BN * 128;
   static constexpr int B_STAGES = 2;
   static constexpr int OFF_RAW = 0;
@@ -97,6 +98,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
         "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
         "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
       : "r"(taddr)
       : "memory");
 }
@@ -154,12 +163,15 @@ __device__ __forceinline__ uint32_t scale_pair_at(uint32_t row, int n) {
 }
 
 template <typename T, int FMT>
-__device__ __forceinline__ void dequant_chunk(uint32_t raw, uint32_t btile, int d, int lane, int rpc, int group_size) {
+__device__ __forceinline__ void dequant_chunk(uint32_t raw, uint32_t btile, int dw, int lane, int rpc, int group_size) {
+  // 16 warps: warp dw -> 16-byte k chunk d = dw & 7 and the pair of 64-column tiles dw >> 3;
+  // lane -> tile of the pair (bit 4), half of the store steps (bit 3), 8-column vector nv (bits 0-2).
   constexpr int BITS = format_bits(FMT);
   constexpr int RAW_W = KT * 16 * BN * BITS / 8;
   constexpr int SROW = format_scale_is_byte(FMT) ? BN : BN * 2;
+  const int d = dw & 7;
   const int kt = d >> 1, half = d & 1;
-  const int sub = lane >> 3, nv = lane & 7;
+  const int sub = (dw >> 3) * 2 + (lane >> 4), nv = lane & 7, sh = (lane >> 3) & 1;
   const int row_local = (rpc == 1) ? 0 : (kt * 16 + half * 8) / group_size;
   const uint32_t srow = raw + RAW_W + row_local * SROW;
   const uint32_t zrow = raw + RAW_W + META + row_local * SROW;
@@ -172,7 +184,24 @@ __device__ __forceinline__ void dequant_chunk(uint32_t raw, uint32_t btile, int 
       const int lk = half * 8 + i;
       w[i] = lds32(raw + kt * 2048 + lk * 128 + ((nv ^ (lk & 7)) << 4) + sub * 4);
     }
-    // za: codes of the columns whose parity equals this lane's nv parity ... zb: the other parity.
+    // scales / zeros of this thread's four columns, fetched before any arithmetic
+    uint32_t sp[4], zp[4];
+#pragma unroll
+    for (int s4 = 0; s4 < 4; ++s4) {
+      const int j = (sh * 4 + s4) ^ nv;
+      const int n = n8 + j;
+      zp[s4] = 0;
+      if constexpr (FMT == kNVFP4) {
+        const int pos = (j & 4) + ((j & 3) == 1 ? 2 : (j & 3) == 2 ? 1 : (j & 3));
+        sp[s4] = fp4_scale_pair<T, FMT>((lds16(srow + ((n8 + pos) & ~1)) >> (8 * (pos & 1))) & 0xffu);
+      } else if constexpr (FMT == kMXFP4) {
+        sp[s4] = fp4_scale_pair<T, FMT>((lds16(srow + (n & ~1)) >> (8 * (n & 1))) & 0xffu);
+      } else {
+        sp[s4] = scale_pair_at<T>(srow, n);
+        if constexpr (format_has_zp(FMT)) zp[s4] = scale_pair_at<T>(zrow, n) ^ 0x80008000u;
+      }
+    }
+    // za: codes of the columns whose parity equals this lane's nv parity; zb: the other parity
     // (low 16 bits of a word = even columns 0,2,4,6; high 16 bits = odd columns 1,3,5,7)
     const uint32_t sel_a = (nv & 1) ? 0x7632u : 0x5410u, sel_b = (nv & 1) ? 0x5410u : 0x7632u;
     uint32_t za[4], zb[4];
@@ -182,24 +211,15 @@ __device__ __forceinline__ void dequant_chunk(uint32_t raw, uint32_t btile, int 
       zb[kp] = prmt(w[2 * kp], w[2 * kp + 1], sel_b);
     }
 #pragma unroll
-    for (int s = 0; s < 8; ++s) {
-      const int j = s ^ nv;                 // column handled in this step
-      const int m = j >> 1;                 // its code index inside the 16-bit half
+    for (int s4 = 0; s4 < 4; ++s4) {
+      const int s = sh * 4 + s4;
+      const int j = s ^ nv;  // column handled in this step
+      const int m = j >> 1;  // its code index inside the 16-bit half
       const int n = n8 + j;
-      uint32_t sp, zp = 0;
-      if constexpr (FMT == kNVFP4) {
-        const int pos = (j & 4) + ((j & 3) == 1 ? 2 : (j & 3) == 2 ? 1 : (j & 3));
-        sp = fp4_scale_pair<T, FMT>(lds16(srow + ((n8 + pos) & ~1)) >> (8 * (pos & 1)) & 0xffu);
-      } else if constexpr (FMT == kMXFP4) {
-        sp = fp4_scale_pair<T, FMT>((lds16(srow + (n & ~1)) >> (8 * (n & 1))) & 0xffu);
-      } else {
-        sp = scale_pair_at<T>(srow, n);
-        if constexpr (format_has_zp(FMT)) zp = scale_pair_at<T>(zrow, n) ^ 0x80008000u;
-      }
       uint32_t v[4];
 #pragma unroll
       for (int kp = 0; kp < 4; ++kp) {
-        const uint32_t z = (s & 1) ? zb[kp] : za[kp];
+        const uint32_t z = (s4 & 1) ? zb[kp] : za[kp];  // s and s4 have the same parity
         uint32_t q;
         if constexpr (FMT == kU4B8 || FMT == kU4) {
           constexpr uint32_t zero = (FMT == kU4B8) ? 8 : 0;
@@ -208,44 +228,49 @@ __device__ __forceinline__ void dequant_chunk(uint32_t raw, uint32_t btile, int 
           q = psub<T>(((z >> (4 * m)) & 0x000f000fu) | (magic | (magic << 16)), c | (c << 16));
         } else {
           const uint32_t t = z << (12 - 4 * m);
-          constexpr int sh = kHalf<T> ? 3 : 6;
-          q = ((t & 0x70007000u) >> sh) | (t & 0x80008000u);
+          constexpr int shf = kHalf<T> ? 3 : 6;
+          q = ((t & 0x70007000u) >> shf) | (t & 0x80008000u);
         }
-        if constexpr (format_has_zp(FMT)) v[kp] = pfma<T>(q, sp, zp);
-        else v[kp] = pmul<T>(q, sp);
+        if constexpr (format_has_zp(FMT)) v[kp] = pfma<T>(q, sp[s4], zp[s4]);
+        else v[kp] = pmul<T>(q, sp[s4]);
       }
       sts128(btile + n * 128 + ((d ^ j) << 4), v[0], v[1], v[2], v[3]);
     }
   } else {
+    // 8-bit: the two lanes that differ in bit 3 take the two 128-byte half lines (columns nv*4 and
+    // (nv + 8)*4 of the tile); each writes its four columns, rotated by nv >> 1.
     const int rot = (nv >> 1) & 3;
+    const int hh = sh;
+    const int n4 = sub * 64 + (nv + 8 * hh) * 4;
+    uint32_t w[8];
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      const int n4 = sub * 64 + (nv + 8 * hh) * 4;
-      uint32_t w[8];
+    for (int i = 0; i < 8; ++i) {
+      const int R = (half * 8 + i) * 2 + hh;
+      w[i] = lds32(raw + kt * 4096 + R * 128 + ((nv ^ (R & 7)) << 4) + sub * 4);
+    }
+    uint32_t sp[4], zp[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int R = (half * 8 + i) * 2 + hh;
-        w[i] = lds32(raw + kt * 4096 + R * 128 + ((nv ^ (R & 7)) << 4) + sub * 4);
+    for (int s = 0; s < 4; ++s) {
+      const int n = n4 + (s ^ rot);
+      sp[s] = scale_pair_at<T>(srow, n);
+      zp[s] = 0;
+      if constexpr (format_has_zp(FMT)) zp[s] = scale_pair_at<T>(zrow, n) ^ 0x80008000u;
+    }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const int j = s ^ rot;                         // column handled in this step
+      const int bp = (j & 1) * 2 + (j >> 1);         // its byte inside the word
+      const uint32_t sel = (uint32_t)bp | ((uint32_t)(4 + bp) << 4);
+      const int n = n4 + j;
+      uint32_t v[4];
+#pragma unroll
+      for (int kp = 0; kp < 4; ++kp) {
+        const uint32_t y = prmt(w[2 * kp], w[2 * kp + 1], sel);  // bytes 0,1 = the code at k0, k1
+        const uint32_t q = value8<T, FMT>(y, 0);
+        if constexpr (format_has_zp(FMT)) v[kp] = pfma<T>(q, sp[s], zp[s]);
+        else v[kp] = pmul<T>(q, sp[s]);
       }
-#pragma unroll
-      for (int s = 0; s < 4; ++s) {
-        const int j = s ^ rot;                         // column handled in this step
-        const int bp = (j & 1) * 2 + (j >> 1);         // its byte inside the word
-        const uint32_t sel = (uint32_t)bp | ((uint32_t)(4 + bp) << 4);
-        const int n = n4 + j;
-        const uint32_t sp = scale_pair_at<T>(srow, n);
-        uint32_t zp = 0;
-        if constexpr (format_has_zp(FMT)) zp = scale_pair_at<T>(zrow, n) ^ 0x80008000u;
-        uint32_t v[4];
-#pragma unroll
-        for (int kp = 0; kp < 4; ++kp) {
-          const uint32_t y = prmt(w[2 * kp], w[2 * kp + 1], sel);  // bytes 0,1 = the code at k0, k1
-          const uint32_t q = value8<T, FMT>(y, 0);
-          if constexpr (format_has_zp(FMT)) v[kp] = pfma<T>(q, sp, zp);
-          else v[kp] = pmul<T>(q, sp);
-        }
-        sts128(btile + n * 128 + ((d ^ (n & 7)) << 4), v[0], v[1], v[2], v[3]);
-      }
+      sts128(btile + n * 128 + ((d ^ (n & 7)) << 4), v[0], v[1], v[2], v[3]);
     }
   }
 }
@@ -400,15 +425,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       for (int h = 0; h < MT; ++h) {
         const int row = mt * 128 * MT + h * 128 + q * 32 + lane;
 #pragma unroll 1
-        for (int cb = 0; cb < BN / 32; ++cb) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + h * 256 + cb * 32, v);
+        for (int cb = 0; cb < BN / 16; ++cb) {
+          uint32_t v[16];
+          tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + h * 256 + cb * 16, v);
           tmem_ld_wait();
-          const int col0 = nt * BN + cb * 32;
+          const int col0 = nt * BN + cb * 16;
           if (row < p.M) {
-            uint32_t o[16];
+            uint32_t o[8];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
+            for (int i = 0; i < 8; ++i) {
               float x0 = __uint_as_float(v[2 * i]) * alpha, x1 = __uint_as_float(v[2 * i + 1]) * alpha;
               if (bias != nullptr) {
                 x0 += to_float<T>(bias[bias_index(col0 + 2 * i)]);
@@ -417,8 +442,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               o[i] = pack_out<T>(x0, x1);
             }
             uint4* dst = reinterpret_cast<uint4*>(C + (int64_t)row * p.N + col0);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
           }
         }
       }
@@ -454,6 +479,317 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   }
 
   // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, NCOLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Grouped (MoE) variant
+// ---------------------------------------------------------------------------------------------------
+// Rows come from `sorted_token_ids`: blocks of `bs` routes, each block belonging to one expert.  A
+// tile is the 128 / bs consecutive blocks that fill the 128 rows of the MMA (96 rows for bs = 48);
+// inside a tile every run of blocks of the same expert is one work item: the whole K loop with that
+// expert's weights, after which the epilogue scatters only the rows of the run (C row = route id,
+// times the router weight when asked).  Activation rows are gathered with cp.async (16 bytes at a
+// time, zero-filled for padding rows) straight into the swizzled operand layout.
+struct MoeParams {
+  const void* a;
+  void* c;
+  const void* bias;
+  const float* global_scale;
+  const int32_t* sorted_ids;
+  const int32_t* expert_ids;
+  const int32_t* num_post_pad;
+  const float* topk_weights;
+  int64_t size_m;
+  int N, K;
+  int num_groups, group_size, rpc;
+  int kc, n_tiles, num_tiles;
+  int num_sorted, num_experts;
+  int bs, blocks_per_tile, top_k, mul_topk;
+  uint32_t raw_tx;
+};
+
+struct ItemIter {
+  int w, total, stride, n_tiles, blocks_per_tile, bs, num_blocks, num_experts;
+  int tile, nt, blk, blk_end;
+  const int32_t* expert_ids;
+  __device__ void init(const MoeParams& p) {
+    stride = gridDim.x;
+    w = (int)blockIdx.x - stride;
+    total = p.num_tiles * p.n_tiles;
+    n_tiles = p.n_tiles;
+    blocks_per_tile = p.blocks_per_tile;
+    bs = p.bs;
+    const int padded = min(p.num_post_pad[0], p.num_sorted);
+    num_blocks = padded / p.bs;
+    num_experts = p.num_experts;
+    expert_ids = p.expert_ids;
+    blk = blk_end = 0;
+    tile = nt = 0;
+  }
+  // Advances to the next run of same-expert blocks; false when this CTA has no more work.
+  __device__ bool next(int& e, int& row_lo, int& row_hi) {
+    for (;;) {
+      if (blk >= blk_end) {
+        w += stride;
+        if (w >= total) return false;
+        tile = w / n_tiles;
+        nt = w - tile * n_tiles;
+        blk = tile * blocks_per_tile;
+        blk_end = min(blk + blocks_per_tile, num_blocks);
+        if (blk >= blk_end) continue;
+      }
+      const int lo = blk;
+      e = expert_ids[blk];
+      ++blk;
+      while (blk < blk_end && expert_ids[blk] == e) ++blk;
+      if (e < 0 || e >= num_experts) continue;
+      row_lo = (lo - tile * blocks_per_tile) * bs;
+      row_hi = (blk - tile * blocks_per_tile) * bs;
+      return true;
+    }
+  }
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename T, int FMT>
+__global__ void __launch_bounds__(THREADS, 1)
+tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
+              const __grid_constant__ CUtensorMap tmZ, const MoeParams p) {
+  constexpr int BITS = format_bits(FMT);
+  using L = TcLayout<BITS, 1, MOE_A_STAGES>;
+  constexpr int RS = L::RAW_STAGES, AS = L::A_STAGES, BS = L::B_STAGES;
+  constexpr int LAG = AS - 1;  // a stage is published once LAG younger copy groups have been issued
+  constexpr uint32_t NCOLS = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar0 = base + L::OFF_BAR;
+  auto raw_full = [&](int s) { return bar0 + 8u * s; };
+  auto raw_empty = [&](int s) { return bar0 + 8u * (RS + s); };
+  auto a_full = [&](int s) { return bar0 + 8u * (2 * RS + s); };
+  auto a_empty = [&](int s) { return bar0 + 8u * (2 * RS + AS + s); };
+  auto b_full = [&](int s) { return bar0 + 8u * (2 * RS + 2 * AS + s); };
+  auto b_empty = [&](int s) { return bar0 + 8u * (2 * RS + 2 * AS + BS + s); };
+  const uint32_t acc_full = bar0 + 8u * (2 * RS + 2 * AS + 2 * BS);
+  const uint32_t acc_empty = acc_full + 8u;
+  const uint32_t tmem_slot = acc_empty + 8u;
+
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    s_abort = 0;
+    for (int s = 0; s < RS; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DQ_WARPS); }
+    for (int s = 0; s < AS; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
+    for (int s = 0; s < BS; ++s) { mbar_init(b_full(s), DQ_WARPS); mbar_init(b_empty(s), 1); }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 4);
+    fence_barrier_init();
+    prefetch_tensormap(&tmW);
+    prefetch_tensormap(&tmS);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, NCOLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  constexpr int ROWS_PER_KT = (BITS == 4) ? 16 : 32;
+  ItemIter iter;
+  iter.init(p);
+  int e = 0, row_lo = 0, row_hi = 0;
+
+  if (warp == 0) {
+    // ---------------- packed-weight producer ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      while (ok && iter.next(e, row_lo, row_hi)) {
+        for (int c = 0; c < p.kc; ++c) {
+          if (!mbar_wait(raw_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 11); ok = false; break; }
+          const uint32_t st = base + L::OFF_RAW + s * L::RAW_BYTES;
+          mbar_arrive_expect_tx(raw_full(s), p.raw_tx);
+          tma_load_4d(st, &tmW, raw_full(s), 0, iter.nt * ROWS_PER_KT, c * KT, e);
+          const int srow = (p.num_groups == 1) ? 0 : (c * BK) / p.group_size;
+          tma_load_3d(st + L::RAW_W, &tmS, raw_full(s), iter.nt * BN, srow, e);
+          if constexpr (format_has_zp(FMT)) tma_load_3d(st + L::RAW_W + META, &tmZ, raw_full(s), iter.nt * BN, srow, e);
+          if (++s == RS) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- activation gather ----------------
+    // Lane l copies rows l, l + 32, l + 64, l + 96.  Copies of a stage are committed as one group;
+    // a stage is published LAG iterations later, once its group has landed.
+    const T* A = reinterpret_cast<const T*>(p.a);
+    int s = 0;
+    uint32_t ph = 0;
+    int issued = 0;
+    bool ok = true;
+    auto publish = [&](int stage) {
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_full(stage));
+    };
+    while (ok && iter.next(e, row_lo, row_hi)) {
+      int64_t src_row[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = lane + 32 * i;
+        const int64_t pos = (int64_t)iter.tile * (iter.blocks_per_tile * iter.bs) + r;
+        int sid = -1;
+        if (r < iter.blocks_per_tile * iter.bs && pos < p.num_sorted) sid = p.sorted_ids[pos];
+        src_row[i] = (sid >= 0 && (int64_t)sid < p.size_m * p.top_k) ? (int64_t)(sid / p.top_k) : -1;
+      }
+      for (int c = 0; c < p.kc; ++c) {
+        if (!mbar_wait(a_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 12); ok = false; break; }
+        const uint32_t st = base + L::OFF_A + s * L::A_BYTES;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = lane + 32 * i;
+          const T* src = A + (src_row[i] >= 0 ? src_row[i] : 0) * (int64_t)p.K + (int64_t)c * BK;
+#pragma unroll
+          for (int c16 = 0; c16 < 8; ++c16) {
+            const bool in = src_row[i] >= 0 && (c * BK + c16 * 8) < p.K;
+            cp_async16(st + r * 128 + ((c16 ^ (r & 7)) << 4), in ? (const void*)(src + c16 * 8) : (const void*)A, in ? 16u : 0u);
+          }
+        }
+        cp_async_commit();
+        ++issued;
+        if (issued > LAG) {
+          cp_async_wait<LAG>();
+          publish((s + AS - LAG) % AS);
+        }
+        if (++s == AS) { s = 0; ph ^= 1u; }
+      }
+    }
+    // drain: publish what is still in flight (at most LAG stages), oldest first
+    cp_async_wait<0>();
+    if (ok) {
+      for (int back = (issued < LAG ? issued : LAG); back >= 1; --back) publish((s + AS - back) % AS);
+    }
+  } else if (warp == 2) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc<T>();
+      int sa = 0, sb = 0;
+      uint32_t pha = 0, phb = 0, phacc = 0;
+      bool ok = true;
+      while (ok && iter.next(e, row_lo, row_hi)) {
+        if (!mbar_wait(acc_empty, phacc ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 13); ok = false; break; }
+        tc_fence_after();
+        for (int c = 0; c < p.kc; ++c) {
+          if (!mbar_wait(a_full(sa), pha, &s_abort) || !mbar_wait(b_full(sb), phb, &s_abort)) {
+            atomicExch(&g_tc_status, 14);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = base + L::OFF_A + sa * L::A_BYTES;
+          const uint32_t b_addr = base + L::OFF_B + sb * L::B_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk)
+            tc_mma_f16(tmem_base, kmajor_sw128_desc(a_addr + kk * 32), kmajor_sw128_desc(b_addr + kk * 32), idesc,
+                       (c > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(a_empty(sa));
+          tc_commit(b_empty(sb));
+          if (++sa == AS) { sa = 0; pha ^= 1u; }
+          if (++sb == BS) { sb = 0; phb ^= 1u; }
+        }
+        if (ok) tc_commit(acc_full);
+        phacc ^= 1u;
+      }
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ---------------- epilogue: scatter the rows of the run ----------------
+    const int q = warp - 4;
+    uint32_t ph = 0;
+    T* C = reinterpret_cast<T*>(p.c);
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    while (iter.next(e, row_lo, row_hi)) {
+      if (!mbar_wait(acc_full, ph, &s_abort)) { atomicExch(&g_tc_status, 15); break; }
+      ph ^= 1u;
+      tc_fence_after();
+      const int r = q * 32 + lane;
+      int sid = -1;
+      if (r >= row_lo && r < row_hi) {
+        const int64_t pos = (int64_t)iter.tile * (iter.blocks_per_tile * iter.bs) + r;
+        if (pos < p.num_sorted) sid = p.sorted_ids[pos];
+        if (sid < 0 || (int64_t)sid >= p.size_m * p.top_k) sid = -1;
+      }
+      float gs = 1.f;
+      if constexpr (FMT == kNVFP4) gs = p.global_scale[e];
+      const float tw = (sid >= 0 && p.mul_topk) ? p.topk_weights[sid] : 1.f;
+      const float bias_mul = (FMT == kNVFP4 && p.mul_topk) ? gs : 1.f;
+#pragma unroll 1
+      for (int cb = 0; cb < BN / 16; ++cb) {
+        uint32_t v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + cb * 16, v);
+        tmem_ld_wait();
+        const int col0 = iter.nt * BN + cb * 16;
+        if (sid >= 0) {
+          uint32_t o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float x0 = __uint_as_float(v[2 * i]) * gs, x1 = __uint_as_float(v[2 * i + 1]) * gs;
+            if (bias != nullptr) {
+              x0 += to_float<T>(bias[(int64_t)e * p.N + bias_index(col0 + 2 * i)]) * bias_mul;
+              x1 += to_float<T>(bias[(int64_t)e * p.N + bias_index(col0 + 2 * i + 1)]) * bias_mul;
+            }
+            o[i] = pack_out<T>(x0 * tw, x1 * tw);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(C + (int64_t)sid * p.N + col0);
+          dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+          dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty);
+    }
+  } else if (warp >= 8) {
+    // ---------------- dequantisation ----------------
+    const int d = warp - 8;
+    int sr = 0, sb = 0;
+    uint32_t phr = 0, phb = 0;
+    bool ok = true;
+    while (ok && iter.next(e, row_lo, row_hi)) {
+      for (int c = 0; c < p.kc; ++c) {
+        if (!mbar_wait(raw_full(sr), phr, &s_abort) || !mbar_wait(b_empty(sb), phb ^ 1u, &s_abort)) {
+          atomicExch(&g_tc_status, 16);
+          ok = false;
+          break;
+        }
+        dequant_chunk<T, FMT>(base + L::OFF_RAW + sr * L::RAW_BYTES, base + L::OFF_B + sb * L::B_BYTES, d, lane,
+                              p.rpc, p.group_size);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(b_full(sb));
+          mbar_arrive(raw_empty(sr));
+        }
+        if (++sr == RS) { sr = 0; phr ^= 1u; }
+        if (++sb == BS) { sb = 0; phb ^= 1u; }
+      }
+    }
+  }
+
   tc_fence_before();
   __syncthreads();
   if (warp == 2) {
@@ -582,11 +918,106 @@ int launch_dtype(const GemmArgs& g) {
   return 1;
 }
 
+
+template <typename T, int FMT>
+int launch_moe(const GemmArgs& g) {
+  constexpr int BITS = format_bits(FMT);
+  using L = TcLayout<BITS, 1, MOE_A_STAGES>;
+  constexpr int SMEM = 1024 + L::TOTAL;
+  static_assert(SMEM <= 227 * 1024, "shared memory budget");
+  const int64_t K = g.size_k, N = g.size_n, E = g.num_experts;
+  const int64_t gs = K / g.num_groups;
+  MoeParams p{};
+  p.a = g.a; p.c = g.c; p.bias = g.bias; p.global_scale = g.global_scale;
+  p.sorted_ids = g.sorted_ids; p.expert_ids = g.expert_ids; p.num_post_pad = g.num_post_pad;
+  p.topk_weights = g.topk_weights;
+  p.size_m = g.size_m; p.N = (int)N; p.K = (int)K;
+  p.num_groups = (int)g.num_groups; p.group_size = (int)gs;
+  p.rpc = (g.num_groups > 1 && gs < BK) ? (int)(BK / gs) : 1;
+  p.kc = (int)((K + BK - 1) / BK);
+  p.n_tiles = (int)(N / BN);
+  p.bs = g.block_size;
+  // Few routes per expert: blocks of different experts cannot share an MMA, so one block per tile
+  // gives every (block, column group) its own CTA.  Many routes per expert: fill the 128 rows.
+  const int64_t routes = g.size_m * g.top_k;
+  p.blocks_per_tile = (routes / E < g.block_size) ? 1 : 128 / g.block_size;
+  p.num_sorted = (int)g.num_sorted;
+  const int64_t blocks = g.num_sorted / g.block_size;
+  p.num_tiles = (int)((blocks + p.blocks_per_tile - 1) / p.blocks_per_tile);
+  p.num_experts = (int)E; p.top_k = g.top_k; p.mul_topk = g.mul_topk;
+  const int srow_bytes = format_scale_is_byte(FMT) ? BN : BN * 2;
+  p.raw_tx = L::RAW_W + p.rpc * srow_bytes * (format_has_zp(FMT) ? 2 : 1);
+  if (p.num_tiles == 0) return 0;
+
+  CUtensorMap tmW, tmS, tmZ;
+  {
+    const int rows_per_kt = (BITS == 4 ? 16 : 32) * p.n_tiles;
+    const uint64_t dims[4] = {32, (uint64_t)rows_per_kt, (uint64_t)(K / 16), (uint64_t)E};
+    const uint64_t strides[3] = {128, (uint64_t)rows_per_kt * 128, (uint64_t)rows_per_kt * 128 * (uint64_t)(K / 16)};
+    const uint32_t box[4] = {32, (uint32_t)(BITS == 4 ? 16 : 32), KT, 1};
+    if (int rc = cached_map(&tmW, MapKey{g.bq, N, K, BITS + 16 * E}, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, g.bq, dims, strides,
+                            box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  {
+    const bool byte_scale = format_scale_is_byte(FMT);
+    const uint64_t es = byte_scale ? 1 : 2;
+    const uint64_t dims[3] = {(uint64_t)N, (uint64_t)g.num_groups, (uint64_t)E};
+    const uint64_t strides[2] = {(uint64_t)N * es, (uint64_t)N * es * (uint64_t)g.num_groups};
+    const uint32_t box[3] = {BN, (uint32_t)p.rpc, 1};
+    const CUtensorMapDataType dt = byte_scale ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+    if (int rc = cached_map(&tmS, MapKey{g.scales, N, g.num_groups, p.rpc * 16 + byte_scale + 1024 * E}, dt, 3, g.scales,
+                            dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+      return rc;
+    tmZ = tmS;
+    if (format_has_zp(FMT)) {
+      if (int rc = cached_map(&tmZ, MapKey{g.zeros, N, g.num_groups, p.rpc * 16 + byte_scale + 1024 * E}, dt, 3, g.zeros,
+                              dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return rc;
+    }
+  }
+  static bool attr_set[64] = {};
+  int dev = 0;
+  MB_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    MB_CUDA(cudaFuncSetAttribute(tc_moe_kernel<T, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    attr_set[dev] = true;
+  }
+  const int64_t work = (int64_t)p.num_tiles * p.n_tiles;
+  const int grid = (int)(work < sm_count() ? work : sm_count());
+  tc_moe_kernel<T, FMT><<<grid, THREADS, SMEM, g.stream>>>(tmW, tmS, tmZ, p);
+  MB_CUDA(cudaGetLastError());
+  count_launches(1);
+  return 0;
+}
+
+template <typename T>
+int launch_moe_dtype(const GemmArgs& g) {
+  switch (g.format) {
+    case kU4B8: return launch_moe<T, kU4B8>(g);
+    case kU4: return launch_moe<T, kU4>(g);
+    case kU8B128: return launch_moe<T, kU8B128>(g);
+    case kU8: return launch_moe<T, kU8>(g);
+    case kFP8: return launch_moe<T, kFP8>(g);
+    case kNVFP4: return launch_moe<T, kNVFP4>(g);
+    case kMXFP4: return launch_moe<T, kMXFP4>(g);
+  }
+  return 1;
+}
 }  // namespace
 
 // Returns 1 when the problem is not one this kernel takes.
 int launch_gemm_tc(const GemmArgs& g) {
-  if (g.sorted_ids != nullptr) return 1;
+  if (g.size_n % BN != 0 || g.size_k % 32 != 0) return 1;
+  if (g.sorted_ids != nullptr) {
+    if (g.num_groups > 1) {
+      const int64_t gs = g.size_k / g.num_groups;
+      if (!(gs == 16 || gs == 32 || gs % BK == 0)) return 1;
+    }
+    if (g.size_k % 8 != 0 || (reinterpret_cast<uintptr_t>(g.a) & 15) != 0) return 1;
+    if (g.act_dtype == MARLIN_B200_F16) return launch_moe_dtype<__half>(g);
+    return launch_moe_dtype<__nv_bfloat16>(g);
+  }
   if (g.size_m <= 0 || g.size_n % BN != 0 || g.size_k % 32 != 0) return 1;
   if (g.num_groups > 1) {
     const int64_t gs = g.size_k / g.num_groups;
