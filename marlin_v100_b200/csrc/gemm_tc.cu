@@ -3,7 +3,7 @@
 //
 // One persistent CTA per SM, 768 threads, warp-specialised:
 //   warp 0      TMA producer of the packed weight chunks (+ their scale / zero-point rows)
-//   warp 1      TMA producer of the activation tiles
+//   warp 1      TMA producer of the activation tiles (grouped kernel: warps 1 and 3 gather rows)
 //   warp 2      allocates tensor memory, issues the MMAs (one thread)
 //   warps 4-7   epilogue: tcgen05.ld the accumulator, bias / nvfp4 global scale, store C
 //   warps 8-23  dequantise: packed codes (shared memory) -> K-major 128-byte-swizzled operand tile
@@ -570,7 +570,6 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   constexpr int BITS = format_bits(FMT);
   using L = TcLayout<BITS, 1, MOE_A_STAGES>;
   constexpr int RS = L::RAW_STAGES, AS = L::A_STAGES, BS = L::B_STAGES;
-  constexpr int LAG = AS - 1;  // a stage is published once LAG younger copy groups have been issued
   constexpr uint32_t NCOLS = 256;
 
   extern __shared__ uint8_t smem_raw[];
@@ -587,11 +586,12 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const uint32_t tmem_slot = acc_empty + 8u;
 
   __shared__ int s_abort;
+  __shared__ int s_row_src[128];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     s_abort = 0;
     for (int s = 0; s < RS; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DQ_WARPS); }
-    for (int s = 0; s < AS; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
+    for (int s = 0; s < AS; ++s) { mbar_init(a_full(s), 64); mbar_init(a_empty(s), 1); }
     for (int s = 0; s < BS; ++s) { mbar_init(b_full(s), DQ_WARPS); mbar_init(b_empty(s), 1); }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 4);
@@ -633,57 +633,52 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 3) {
     // ---------------- activation gather ----------------
-    // Lane l copies rows l, l + 32, l + 64, l + 96.  Copies of a stage are committed as one group;
-    // a stage is published LAG iterations later, once its group has landed.
+    // Two warps, 64 rows each.  Eight consecutive lanes copy the eight 16-byte pieces of one row's
+    // 128-byte segment (one coalesced line per row), four rows per instruction.  The source row of
+    // every tile row is looked up once per work item and kept in shared memory.  Completion is
+    // reported by the copies themselves: every lane attaches an arrive to its outstanding copies
+    // (cp.async.mbarrier.arrive.noinc), so the stage's barrier (64 arrivals) completes when all
+    // 64 lanes' data has landed, and the gather warps never wait for their own copies.
     const T* A = reinterpret_cast<const T*>(p.a);
+    const int gw = warp >> 1;                 // 0 or 1: which half of the rows
+    int* row_src = s_row_src + gw * 64;
+    const int c16 = lane & 7, rsub = lane >> 3;
     int s = 0;
     uint32_t ph = 0;
-    int issued = 0;
     bool ok = true;
-    auto publish = [&](int stage) {
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(a_full(stage));
-    };
     while (ok && iter.next(e, row_lo, row_hi)) {
-      int64_t src_row[4];
+      __syncwarp();
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = lane + 32 * i;
+      for (int i = 0; i < 2; ++i) {
+        const int r = gw * 64 + lane + 32 * i;
         const int64_t pos = (int64_t)iter.tile * (iter.blocks_per_tile * iter.bs) + r;
         int sid = -1;
         if (r < iter.blocks_per_tile * iter.bs && pos < p.num_sorted) sid = p.sorted_ids[pos];
-        src_row[i] = (sid >= 0 && (int64_t)sid < p.size_m * p.top_k) ? (int64_t)(sid / p.top_k) : -1;
+        row_src[lane + 32 * i] = (sid >= 0 && (int64_t)sid < p.size_m * p.top_k) ? sid / p.top_k : -1;
       }
+      __syncwarp();
       for (int c = 0; c < p.kc; ++c) {
         if (!mbar_wait(a_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 12); ok = false; break; }
         const uint32_t st = base + L::OFF_A + s * L::A_BYTES;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = lane + 32 * i;
-          const T* src = A + (src_row[i] >= 0 ? src_row[i] : 0) * (int64_t)p.K + (int64_t)c * BK;
-#pragma unroll
-          for (int c16 = 0; c16 < 8; ++c16) {
-            const bool in = src_row[i] >= 0 && (c * BK + c16 * 8) < p.K;
-            cp_async16(st + r * 128 + ((c16 ^ (r & 7)) << 4), in ? (const void*)(src + c16 * 8) : (const void*)A, in ? 16u : 0u);
-          }
+        const bool k_in = (c * BK + c16 * 8) < p.K;
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) {
+          const int rl = 4 * i + rsub;          // row inside this warp's half
+          const int r = gw * 64 + rl;
+          const int src = row_src[rl];
+          const bool in = src >= 0 && k_in;
+          const T* sp = A + (int64_t)(in ? src : 0) * p.K + (int64_t)c * BK + c16 * 8;
+          cp_async16(st + r * 128 + ((c16 ^ (r & 7)) << 4), in ? (const void*)sp : (const void*)A, in ? 16u : 0u);
         }
-        cp_async_commit();
-        ++issued;
-        if (issued > LAG) {
-          cp_async_wait<LAG>();
-          publish((s + AS - LAG) % AS);
-        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(a_full(s)) : "memory");
         if (++s == AS) { s = 0; ph ^= 1u; }
       }
     }
-    // drain: publish what is still in flight (at most LAG stages), oldest first
+    // every issued copy must have landed before the CTA may exit
+    cp_async_commit();
     cp_async_wait<0>();
-    if (ok) {
-      for (int back = (issued < LAG ? issued : LAG); back >= 1; --back) publish((s + AS - back) % AS);
-    }
   } else if (warp == 2) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
