@@ -135,8 +135,9 @@ int marlin_b200_gemm_static_scratch(const void* a, void* c, const int32_t* b_q_w
  * num_tokens_past_padded int32 [1], read on the device; topk_weights fp32 [size_m * top_k].
  * moe_block_size in {8, 16, 32, 48, 64}.
  * -------------------------------------------------------------------------------------------- */
-int64_t marlin_b200_moe_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k,
-                                           int64_t top_k, int format);
+/* Scratch for marlin_b200_moe_gemm: room for the activation rows copied into sorted order,
+ * num_sorted * size_k * 2 bytes (0 when the shape is served by the kernel that needs none). */
+int64_t marlin_b200_moe_gemm_scratch_bytes(int64_t num_sorted, int64_t size_n, int64_t size_k, int format);
 
 int marlin_b200_moe_gemm(const void* a, void* c, const int32_t* b_q_weight, const void* b_scales,
                          const void* b_zeros, const void* b_bias, const float* global_scale,

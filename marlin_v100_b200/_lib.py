@@ -26,7 +26,7 @@ SIGNATURES = {
                                 _i64, _vp, _i64, _vp]),
     "marlin_b200_gemm_static_scratch": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _i64, _i64, _i64,
                                                _i64, _i64, _vp]),
-    "marlin_b200_moe_gemm_scratch_bytes": (_i64, [_i64, _i64, _i64, _i64, _int]),
+    "marlin_b200_moe_gemm_scratch_bytes": (_i64, [_i64, _i64, _i64, _int]),
     "marlin_b200_moe_gemm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                     _int, _int, _int, _int, _int, _i64, _i64, _i64, _i64, _vp, _i64,
                                     _vp]),

@@ -155,7 +155,10 @@ extern "C" int marlin_b200_gemm(const void* a, void* c, const int32_t* b_q_weigh
   return dispatch(g);
 }
 
-extern "C" int64_t marlin_b200_moe_gemm_scratch_bytes(int64_t, int64_t, int64_t, int64_t, int) { return 0; }
+extern "C" int64_t marlin_b200_moe_gemm_scratch_bytes(int64_t num_sorted, int64_t size_n, int64_t size_k, int) {
+  if (size_n % 256 != 0 || size_k % 64 != 0) return 0;  // served by the shape-agnostic kernel
+  return num_sorted * size_k * 2;
+}
 
 extern "C" int marlin_b200_moe_gemm(const void* a, void* c, const int32_t* b_q_weight,
                                     const void* b_scales, const void* b_zeros, const void* b_bias,

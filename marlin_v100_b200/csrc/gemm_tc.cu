@@ -18,6 +18,9 @@
 //   A ring     : TMA -> MMA                          (a_full / a_empty via tcgen05.commit)
 //   B ring     : dequant warps -> MMA                (b_full / b_empty via tcgen05.commit)
 //   accumulator: MMA -> epilogue -> MMA              (acc_full via tcgen05.commit / acc_empty)
+//
+// Compiling with -DMB_TC_PROFILE adds per-role wait-cycle counters for CTA 0 and a debug entry point
+// that reads them; release builds carry neither.
 #include <mutex>
 #include <unordered_map>
 
@@ -36,13 +39,16 @@ constexpr int KT = 4;            // k-tiles of 16 per chunk
 constexpr int META = 2048;       // bytes reserved for the scale rows of a chunk (and again for zeros)
 constexpr int THREADS = 768;
 constexpr int DQ_WARPS = 16;
-constexpr int MOE_A_STAGES = 6;  // the gathered activation ring is deeper: gathers have a long latency
+constexpr int MOE_A_STAGES = 4;  // gathered activation ring of the grouped kernel
 
 template <int BITS, int MT, int AST = 3>
 struct TcLayout {
   static constexpr int RAW_W = KT * 16 * BN * BITS / 8;  // 8 KiB / 16 KiB
   static constexpr int RAW_BYTES = RAW_W + 2 * META;
-  static constexpr int RAW_STAGES = BITS == 4 ? 3 : 2;
+  // as deep as shared memory allows: with few row tiles the kernel streams weights and the ring
+  // depth is what hides the HBM latency
+  static constexpr int RAW_STAGES = (AST != 3) ? (BITS == 4 ? 6 : 4)          // grouped kernel
+                                    : (MT == 1 ? (BITS == 4 ? 8 : 5) : (BITS == 4 ? 5 : 3));
   static constexpr int A_BYTES = MT * 128 * 128;
   static constexpr int A_STAGES = AST;
   static constexpr int B_BYTES = BN * 128;
@@ -67,6 +73,16 @@ struct TcParams {
 };
 
 __device__ int g_tc_status = 0;
+
+#ifdef MB_TC_PROFILE
+// Per-role wait-cycle counters of CTA 0 (debug builds only): [role][slot]
+__device__ unsigned long long g_tc_prof[8][4];
+#define PROF_T0() const long long prof_t0__ = clock64()
+#define PROF_ADD(role, slot) if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_tc_prof[role][slot], (unsigned long long)(clock64() - prof_t0__))
+#else
+#define PROF_T0()
+#define PROF_ADD(role, slot)
+#endif
 
 // ---- tcgen05 wrappers -----------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {
@@ -514,6 +530,27 @@ struct MoeParams {
   uint32_t raw_tx;
 };
 
+// Copies the activation rows into the order of sorted_token_ids (row pos <- A[sid / top_k], zeros for
+// padding entries), 16 bytes per thread step, for the padded length only.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_gather_rows_kernel(const T* __restrict__ a, T* __restrict__ out,
+                                                              const int32_t* __restrict__ sorted_ids,
+                                                              const int32_t* __restrict__ num_post_pad,
+                                                              int num_sorted, int64_t size_m, int top_k, int K) {
+  const int vec_per_row = K / 8;
+  const int rows = min(num_post_pad[0], num_sorted);
+  const int64_t total = (int64_t)rows * vec_per_row;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int pos = (int)(idx / vec_per_row), v = (int)(idx % vec_per_row);
+    const int sid = sorted_ids[pos];
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (sid >= 0 && (int64_t)sid < size_m * top_k)
+      val = *reinterpret_cast<const uint4*>(a + (int64_t)(sid / top_k) * K + v * 8);
+    *reinterpret_cast<uint4*>(out + (int64_t)pos * K + v * 8) = val;
+  }
+}
+
 struct ItemIter {
   int w, total, stride, n_tiles, blocks_per_tile, bs, num_blocks, num_experts;
   int tile, nt, blk, blk_end;
@@ -565,8 +602,8 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 template <typename T, int FMT>
 __global__ void __launch_bounds__(THREADS, 1)
-tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
-              const __grid_constant__ CUtensorMap tmZ, const MoeParams p) {
+tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
+              const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ, const MoeParams p) {
   constexpr int BITS = format_bits(FMT);
   using L = TcLayout<BITS, 1, MOE_A_STAGES>;
   constexpr int RS = L::RAW_STAGES, AS = L::A_STAGES, BS = L::B_STAGES;
@@ -586,17 +623,17 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const uint32_t tmem_slot = acc_empty + 8u;
 
   __shared__ int s_abort;
-  __shared__ int s_row_src[128];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     s_abort = 0;
     for (int s = 0; s < RS; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DQ_WARPS); }
-    for (int s = 0; s < AS; ++s) { mbar_init(a_full(s), 64); mbar_init(a_empty(s), 1); }
+    for (int s = 0; s < AS; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
     for (int s = 0; s < BS; ++s) { mbar_init(b_full(s), DQ_WARPS); mbar_init(b_empty(s), 1); }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 4);
     fence_barrier_init();
     prefetch_tensormap(&tmW);
+    prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmS);
   }
   if (warp == 2) {
@@ -622,63 +659,43 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       bool ok = true;
       while (ok && iter.next(e, row_lo, row_hi)) {
         for (int c = 0; c < p.kc; ++c) {
+          { PROF_T0();
           if (!mbar_wait(raw_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 11); ok = false; break; }
+          PROF_ADD(0, 0); }
           const uint32_t st = base + L::OFF_RAW + s * L::RAW_BYTES;
           mbar_arrive_expect_tx(raw_full(s), p.raw_tx);
-          tma_load_4d(st, &tmW, raw_full(s), 0, iter.nt * ROWS_PER_KT, c * KT, e);
-          const int srow = (p.num_groups == 1) ? 0 : (c * BK) / p.group_size;
-          tma_load_3d(st + L::RAW_W, &tmS, raw_full(s), iter.nt * BN, srow, e);
-          if constexpr (format_has_zp(FMT)) tma_load_3d(st + L::RAW_W + META, &tmZ, raw_full(s), iter.nt * BN, srow, e);
+          // experts are stacked along the k-tile rows (weights) and along the group rows (scales)
+          tma_load_3d(st, &tmW, raw_full(s), 0, iter.nt * ROWS_PER_KT, e * (p.K / 16) + c * KT);
+          const int srow = e * p.num_groups + ((p.num_groups == 1) ? 0 : (c * BK) / p.group_size);
+          tma_load_2d(st + L::RAW_W, &tmS, raw_full(s), iter.nt * BN, srow);
+          if constexpr (format_has_zp(FMT)) tma_load_2d(st + L::RAW_W + META, &tmZ, raw_full(s), iter.nt * BN, srow);
           if (++s == RS) { s = 0; ph ^= 1u; }
         }
       }
     }
-  } else if (warp == 1 || warp == 3) {
-    // ---------------- activation gather ----------------
-    // Two warps, 64 rows each.  Eight consecutive lanes copy the eight 16-byte pieces of one row's
-    // 128-byte segment (one coalesced line per row), four rows per instruction.  The source row of
-    // every tile row is looked up once per work item and kept in shared memory.  Completion is
-    // reported by the copies themselves: every lane attaches an arrive to its outstanding copies
-    // (cp.async.mbarrier.arrive.noinc), so the stage's barrier (64 arrivals) completes when all
-    // 64 lanes' data has landed, and the gather warps never wait for their own copies.
-    const T* A = reinterpret_cast<const T*>(p.a);
-    const int gw = warp >> 1;                 // 0 or 1: which half of the rows
-    int* row_src = s_row_src + gw * 64;
-    const int c16 = lane & 7, rsub = lane >> 3;
-    int s = 0;
-    uint32_t ph = 0;
-    bool ok = true;
-    while (ok && iter.next(e, row_lo, row_hi)) {
-      __syncwarp();
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int r = gw * 64 + lane + 32 * i;
-        const int64_t pos = (int64_t)iter.tile * (iter.blocks_per_tile * iter.bs) + r;
-        int sid = -1;
-        if (r < iter.blocks_per_tile * iter.bs && pos < p.num_sorted) sid = p.sorted_ids[pos];
-        row_src[lane + 32 * i] = (sid >= 0 && (int64_t)sid < p.size_m * p.top_k) ? sid / p.top_k : -1;
-      }
-      __syncwarp();
-      for (int c = 0; c < p.kc; ++c) {
-        if (!mbar_wait(a_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 12); ok = false; break; }
-        const uint32_t st = base + L::OFF_A + s * L::A_BYTES;
-        const bool k_in = (c * BK + c16 * 8) < p.K;
-#pragma unroll 4
-        for (int i = 0; i < 16; ++i) {
-          const int rl = 4 * i + rsub;          // row inside this warp's half
-          const int r = gw * 64 + rl;
-          const int src = row_src[rl];
-          const bool in = src >= 0 && k_in;
-          const T* sp = A + (int64_t)(in ? src : 0) * p.K + (int64_t)c * BK + c16 * 8;
-          cp_async16(st + r * 128 + ((c16 ^ (r & 7)) << 4), in ? (const void*)sp : (const void*)A, in ? 16u : 0u);
+  } else if (warp == 1) {
+    // ---------------- activation producer ----------------
+    // The rows were copied into sorted order by moe_gather_rows_kernel, so a tile's rows are
+    // contiguous and one TMA box load per chunk feeds the MMA, exactly as in the dense kernel.
+    // (Gathering inside this kernel was measured and rejected: cp.async copies are capped by the
+    // number of copies the load/store unit keeps in flight - about 128 cycles per warp instruction -
+    // and TMA gather4 loads cost about 100 cycles of issue time per 4 rows; both starve the MMA.)
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      while (ok && iter.next(e, row_lo, row_hi)) {
+        const int row0 = iter.tile * (iter.blocks_per_tile * iter.bs);
+        for (int c = 0; c < p.kc; ++c) {
+          { PROF_T0();
+          if (!mbar_wait(a_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 12); ok = false; break; }
+          PROF_ADD(1, 0); }
+          mbar_arrive_expect_tx(a_full(s), L::A_BYTES);
+          tma_load_2d(base + L::OFF_A + s * L::A_BYTES, &tmA, a_full(s), c * BK, row0);
+          if (++s == AS) { s = 0; ph ^= 1u; }
         }
-        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(a_full(s)) : "memory");
-        if (++s == AS) { s = 0; ph ^= 1u; }
       }
     }
-    // every issued copy must have landed before the CTA may exit
-    cp_async_commit();
-    cp_async_wait<0>();
   } else if (warp == 2) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
@@ -690,11 +707,12 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (!mbar_wait(acc_empty, phacc ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 13); ok = false; break; }
         tc_fence_after();
         for (int c = 0; c < p.kc; ++c) {
-          if (!mbar_wait(a_full(sa), pha, &s_abort) || !mbar_wait(b_full(sb), phb, &s_abort)) {
-            atomicExch(&g_tc_status, 14);
-            ok = false;
-            break;
-          }
+          { PROF_T0();
+          if (!mbar_wait(a_full(sa), pha, &s_abort)) { atomicExch(&g_tc_status, 14); ok = false; break; }
+          PROF_ADD(2, 0); }
+          { PROF_T0();
+          if (!mbar_wait(b_full(sb), phb, &s_abort)) { atomicExch(&g_tc_status, 14); ok = false; break; }
+          PROF_ADD(2, 1); }
           tc_fence_after();
           const uint32_t a_addr = base + L::OFF_A + sa * L::A_BYTES;
           const uint32_t b_addr = base + L::OFF_B + sb * L::B_BYTES;
@@ -766,15 +784,19 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     bool ok = true;
     while (ok && iter.next(e, row_lo, row_hi)) {
       for (int c = 0; c < p.kc; ++c) {
-        if (!mbar_wait(raw_full(sr), phr, &s_abort) || !mbar_wait(b_empty(sb), phb ^ 1u, &s_abort)) {
-          atomicExch(&g_tc_status, 16);
-          ok = false;
-          break;
-        }
+        { PROF_T0();
+        if (!mbar_wait(raw_full(sr), phr, &s_abort)) { atomicExch(&g_tc_status, 16); ok = false; break; }
+        if (d == 0) PROF_ADD(3, 0); }
+        { PROF_T0();
+        if (!mbar_wait(b_empty(sb), phb ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 16); ok = false; break; }
+        if (d == 0) PROF_ADD(3, 1); }
+        PROF_T0();
         dequant_chunk<T, FMT>(base + L::OFF_RAW + sr * L::RAW_BYTES, base + L::OFF_B + sb * L::B_BYTES, d, lane,
                               p.rpc, p.group_size);
+        if (d == 0) PROF_ADD(3, 2);
         fence_proxy_async();
         __syncwarp();
+        if (d == 0) PROF_ADD(3, 3);
         if (lane == 0) {
           mbar_arrive(b_full(sb));
           mbar_arrive(raw_empty(sr));
@@ -944,29 +966,51 @@ int launch_moe(const GemmArgs& g) {
   p.raw_tx = L::RAW_W + p.rpc * srow_bytes * (format_has_zp(FMT) ? 2 : 1);
   if (p.num_tiles == 0) return 0;
 
-  CUtensorMap tmW, tmS, tmZ;
+  CUtensorMap tmW, tmA, tmS, tmZ;
+  {
+    // activation rows in sorted order live in the scratch buffer
+    const int64_t need = (int64_t)g.num_sorted * K * 2;
+    if (g.scratch == nullptr || g.scratch_bytes < need) {
+      set_error("moe scratch buffer too small: %lld bytes given, %lld needed", (long long)g.scratch_bytes, (long long)need);
+      return MARLIN_B200_ESCRATCH;
+    }
+    const int64_t vecs = (int64_t)g.num_sorted * (K / 8);
+    const int64_t want = (vecs + 255) / 256;
+    const int gblocks = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
+    moe_gather_rows_kernel<T><<<gblocks, 256, 0, g.stream>>>(reinterpret_cast<const T*>(g.a), reinterpret_cast<T*>(g.scratch),
+                                                            g.sorted_ids, g.num_post_pad, (int)g.num_sorted, g.size_m,
+                                                            g.top_k, (int)K);
+    MB_CUDA(cudaGetLastError());
+    count_launches(1);
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)g.num_sorted};
+    const uint64_t strides[1] = {(uint64_t)K * 2};
+    const uint32_t box[2] = {BK, 128};
+    if (int rc = encode_tensor_map(&tmA, kHalf<T> ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                   g.scratch, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
   {
     const int rows_per_kt = (BITS == 4 ? 16 : 32) * p.n_tiles;
-    const uint64_t dims[4] = {32, (uint64_t)rows_per_kt, (uint64_t)(K / 16), (uint64_t)E};
-    const uint64_t strides[3] = {128, (uint64_t)rows_per_kt * 128, (uint64_t)rows_per_kt * 128 * (uint64_t)(K / 16)};
-    const uint32_t box[4] = {32, (uint32_t)(BITS == 4 ? 16 : 32), KT, 1};
-    if (int rc = cached_map(&tmW, MapKey{g.bq, N, K, BITS + 16 * E}, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, g.bq, dims, strides,
+    const uint64_t dims[3] = {32, (uint64_t)rows_per_kt, (uint64_t)(K / 16) * (uint64_t)E};
+    const uint64_t strides[2] = {128, (uint64_t)rows_per_kt * 128};
+    const uint32_t box[3] = {32, (uint32_t)(BITS == 4 ? 16 : 32), KT};
+    if (int rc = cached_map(&tmW, MapKey{g.bq, N, K, BITS + 16 * E}, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.bq, dims, strides,
                             box, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   }
   {
     const bool byte_scale = format_scale_is_byte(FMT);
     const uint64_t es = byte_scale ? 1 : 2;
-    const uint64_t dims[3] = {(uint64_t)N, (uint64_t)g.num_groups, (uint64_t)E};
-    const uint64_t strides[2] = {(uint64_t)N * es, (uint64_t)N * es * (uint64_t)g.num_groups};
-    const uint32_t box[3] = {BN, (uint32_t)p.rpc, 1};
+    const uint64_t dims[2] = {(uint64_t)N, (uint64_t)g.num_groups * (uint64_t)E};
+    const uint64_t strides[1] = {(uint64_t)N * es};
+    const uint32_t box[2] = {BN, (uint32_t)p.rpc};
     const CUtensorMapDataType dt = byte_scale ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
-    if (int rc = cached_map(&tmS, MapKey{g.scales, N, g.num_groups, p.rpc * 16 + byte_scale + 1024 * E}, dt, 3, g.scales,
+    if (int rc = cached_map(&tmS, MapKey{g.scales, N, g.num_groups, p.rpc * 16 + byte_scale + 1024 * E}, dt, 2, g.scales,
                             dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
     tmZ = tmS;
     if (format_has_zp(FMT)) {
-      if (int rc = cached_map(&tmZ, MapKey{g.zeros, N, g.num_groups, p.rpc * 16 + byte_scale + 1024 * E}, dt, 3, g.zeros,
+      if (int rc = cached_map(&tmZ, MapKey{g.zeros, N, g.num_groups, p.rpc * 16 + byte_scale + 1024 * E}, dt, 2, g.zeros,
                               dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
         return rc;
     }
@@ -980,7 +1024,7 @@ int launch_moe(const GemmArgs& g) {
   }
   const int64_t work = (int64_t)p.num_tiles * p.n_tiles;
   const int grid = (int)(work < sm_count() ? work : sm_count());
-  tc_moe_kernel<T, FMT><<<grid, THREADS, SMEM, g.stream>>>(tmW, tmS, tmZ, p);
+  tc_moe_kernel<T, FMT><<<grid, THREADS, SMEM, g.stream>>>(tmW, tmA, tmS, tmZ, p);
   MB_CUDA(cudaGetLastError());
   count_launches(1);
   return 0;
@@ -1009,7 +1053,8 @@ int launch_gemm_tc(const GemmArgs& g) {
       const int64_t gs = g.size_k / g.num_groups;
       if (!(gs == 16 || gs == 32 || gs % BK == 0)) return 1;
     }
-    if (g.size_k % 8 != 0 || (reinterpret_cast<uintptr_t>(g.a) & 15) != 0) return 1;
+    // experts are stacked along K in the tensor maps, so a K tail would read the next expert
+    if (g.size_k % BK != 0 || (reinterpret_cast<uintptr_t>(g.a) & 15) != 0) return 1;
     if (g.act_dtype == MARLIN_B200_F16) return launch_moe_dtype<__half>(g);
     return launch_moe_dtype<__nv_bfloat16>(g);
   }
@@ -1023,3 +1068,14 @@ int launch_gemm_tc(const GemmArgs& g) {
 }
 
 }  // namespace mb200
+
+#ifdef MB_TC_PROFILE
+extern "C" int marlin_b200_debug_tc_prof(unsigned long long* out32, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out32, mb200::g_tc_prof, sizeof(unsigned long long) * 32);
+  if (reset) {
+    unsigned long long z[32] = {};
+    cudaMemcpyToSymbol(mb200::g_tc_prof, z, sizeof(z));
+  }
+  return (int)e;
+}
+#endif

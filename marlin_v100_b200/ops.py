@@ -363,7 +363,7 @@ def moe_wna16_marlin_gemm(input: torch.Tensor, output: torch.Tensor | None, b_qw
         _check(topk_weights.numel() >= size_m * top_k, "topk_weights has fewer than size_m * top_k entries")
         num_sorted = sorted_token_ids.numel()
 
-        nbytes = lib.marlin_b200_moe_gemm_scratch_bytes(size_m, size_n, size_k, top_k, fmt)
+        nbytes = lib.marlin_b200_moe_gemm_scratch_bytes(num_sorted, size_n, size_k, fmt)
         scratch = _scratch(nbytes, a.device)
         _lib.check(lib.marlin_b200_moe_gemm(
             _ptr(a), _ptr(c), _ptr(b_qweight), _ptr(b_scales), _ptr(b_qzeros) if has_zp else None,
