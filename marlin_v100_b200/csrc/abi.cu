@@ -105,6 +105,10 @@ int dispatch(const GemmArgs& g) {
     const int rc = launch_gemm_tc(g);
     if (rc <= 0) return rc;  // handled (0) or failed (<0)
   }
+  if (g.size_m <= 16) {
+    const int rc = launch_gemm_decode_tc(g);  // tensor-memory operand kernel (4-bit integer formats)
+    if (rc <= 0) return rc;
+  }
   const int rc = launch_gemm_decode(g);
   if (rc <= 0) return rc;
   return launch_gemm_generic(g);

@@ -163,6 +163,7 @@ struct GemmArgs {
 int launch_gemm_generic(const GemmArgs& g);
 int launch_gemm_decode(const GemmArgs& g);          // returns 1 if the shape is not handled
 int64_t gemm_decode_scratch_bytes(int64_t m, int64_t n, int64_t k, int format);
+int launch_gemm_decode_tc(const GemmArgs& g);       // returns 1 if the shape is not handled
 int launch_gemm_tc(const GemmArgs& g);              // returns 1 if the shape is not handled
 
 }  // namespace mb200

@@ -834,10 +834,11 @@ bool decode_accepts(int64_t m, int64_t n, int64_t k, int64_t num_groups) {
 }  // namespace
 
 int64_t gemm_decode_scratch_bytes(int64_t m, int64_t n, int64_t k, int format) {
-  (void)format; (void)k;
+  (void)format;
   if (m <= 0 || n % GROUP_N != 0) return 0;
-  // two partial slots of 16 x 256 floats per persistent CTA
-  return (int64_t)sm_count() * 2 * 16 * GROUP_N * (int64_t)sizeof(float);
+  // two partial slots of 16 x 256 floats per persistent CTA, then (tensor-memory decode kernel) the
+  // three 8-bit digit planes of 16 token rows and their 16 row factors
+  return (int64_t)sm_count() * 2 * 16 * GROUP_N * (int64_t)sizeof(float) + 48 * k + 256;
 }
 
 int launch_gemm_decode(const GemmArgs& g) {
