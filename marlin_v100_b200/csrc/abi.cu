@@ -105,8 +105,11 @@ int dispatch(const GemmArgs& g) {
     const int rc = launch_gemm_tc(g);
     if (rc <= 0) return rc;  // handled (0) or failed (<0)
   }
-  if (g.size_m <= 16) {
-    const int rc = launch_gemm_decode_tc(g);  // tensor-memory operand kernel (4-bit integer formats)
+  // Integer-MMA decode kernel (4-bit integer formats, weights through tensor memory): measured ahead of
+  // the register-fragment kernel only for 9-16 rows on large matrices (54 vs 57 us at K = 8192,
+  // N = 28672), behind it for fewer rows and for small matrices, where its two helper launches weigh.
+  if (g.size_m > 8 && g.size_m <= 16 && g.size_k * g.size_n >= (1ll << 27)) {
+    const int rc = launch_gemm_decode_tc(g);
     if (rc <= 0) return rc;
   }
   const int rc = launch_gemm_decode(g);

@@ -41,6 +41,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// (A suspend-time hint on try_wait and a nanosleep between polls were both measured on the decode
+// kernel: the first cost 10 %, the second changed nothing.)
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(

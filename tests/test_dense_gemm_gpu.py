@@ -133,6 +133,40 @@ def test_linearity_full_size():
     assert torch.equal(f(a1), y1)
 
 
+@pytest.mark.parametrize("m", [9, 16])
+@pytest.mark.parametrize("fmt,dtype,group", [("u4b8", torch.float16, 128), ("u4", torch.bfloat16, 128),
+                                             ("u4b8", torch.bfloat16, -1), ("u4", torch.float16, 1024)])
+def test_large_matrix_9_to_16_rows(fmt, dtype, m, group):
+    """K * N = 2^27 with 9-16 rows is served by the integer-MMA kernel (codes as bytes in tensor memory,
+    activations as 7-bit digit planes): parity against (q - zero) * scale in fp32, all columns."""
+    k, n = 8192, 16384
+    g = torch.Generator().manual_seed(5)
+    q = torch.randint(0, 16, (k, n), generator=g, dtype=torch.int32)
+    packed = mo.marlin_pack(q, 4).cuda()
+    ng = 1 if group == -1 else k // group
+    scales = (torch.rand(ng, n, generator=g) * 0.01 + 0.001).to(dtype)
+    a = torch.randn(m, k, generator=g).to(dtype)
+    # a few large activations: the digit planes are relative to the row maximum
+    a[:, 7] *= 40.0
+    zeros = None
+    if fmt == "u4":
+        zeros = (torch.randint(0, 16, (ng, n), generator=g).float() * scales.float()).to(dtype)
+    ops = _ops()
+    ws = torch.empty(0, dtype=torch.int32, device="cuda")
+    out = ops.marlin_gemm(a.cuda(), None, packed, None, scales.cuda(), None, None,
+                          None if zeros is None else zeros.cuda(), None, None, ws,
+                          mo.TYPE_U4 if fmt == "u4" else mo.TYPE_U4B8, m, n, k, True, False, True, zeros is not None)
+    rep = k // ng
+    sc = scales.cuda().float().repeat_interleave(rep, dim=0)
+    w = q.cuda().float()
+    if fmt == "u4":
+        w = w * sc - zeros.cuda().float().repeat_interleave(rep, dim=0)
+    else:
+        w = (w - 8.0) * sc
+    ref = a.cuda().float() @ w
+    check(out, ref.cpu())
+
+
 @pytest.mark.parametrize("kw,match", [
     (dict(g_idx=True), "does not support act_order g_idx"),
     (dict(perm=True), "does not support act_order perm"),
