@@ -537,14 +537,15 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <typename T, int FMT>
+template <typename T, int FMT, int MT>
 __global__ void __launch_bounds__(THREADS, 1)
 tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
               const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ, const MoeParams p) {
   constexpr int BITS = format_bits(FMT);
-  using L = TcLayout<BITS, 1, MOE_A_STAGES>;
+  // MT = 2: 256-row tiles whose two halves share every dequantised B tile (ring depths of the dense kernel)
+  using L = TcLayout<BITS, MT, MT == 1 ? MOE_A_STAGES : 3>;
   constexpr int RS = L::RAW_STAGES, AS = L::A_STAGES, BS = L::B_STAGES;
-  constexpr uint32_t NCOLS = 256;
+  constexpr uint32_t NCOLS = 256 * MT;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -654,9 +655,13 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           const uint32_t a_addr = base + L::OFF_A + sa * L::A_BYTES;
           const uint32_t b_addr = base + L::OFF_B + sb * L::B_BYTES;
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk)
-            tc_mma_f16(tmem_base, kmajor_sw128_desc(a_addr + kk * 32), kmajor_sw128_desc(b_addr + kk * 32), idesc,
-                       (c > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t bdesc = kmajor_sw128_desc(b_addr + kk * 32);
+#pragma unroll
+            for (int h = 0; h < MT; ++h)
+              tc_mma_f16(tmem_base + h * 256, kmajor_sw128_desc(a_addr + h * (128 * 128) + kk * 32), bdesc, idesc,
+                         (c > 0 || kk > 0) ? 1u : 0u);
+          }
           tc_commit(a_empty(sa));
           tc_commit(b_empty(sb));
           if (++sa == AS) { sa = 0; pha ^= 1u; }
@@ -676,37 +681,42 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       if (!mbar_wait(acc_full, ph, &s_abort)) { atomicExch(&g_tc_status, 15); break; }
       ph ^= 1u;
       tc_fence_after();
-      const int r = q * 32 + lane;
-      int sid = -1;
-      if (r >= row_lo && r < row_hi) {
-        const int64_t pos = (int64_t)iter.tile * (iter.blocks_per_tile * iter.bs) + r;
-        if (pos < p.num_sorted) sid = p.sorted_ids[pos];
-        if (sid < 0 || (int64_t)sid >= p.size_m * p.top_k) sid = -1;
-      }
       float gs = 1.f;
       if constexpr (FMT == kNVFP4) gs = p.global_scale[e];
-      const float tw = (sid >= 0 && p.mul_topk) ? p.topk_weights[sid] : 1.f;
       const float bias_mul = (FMT == kNVFP4 && p.mul_topk) ? gs : 1.f;
 #pragma unroll 1
-      for (int cb = 0; cb < BN / 16; ++cb) {
-        uint32_t v[16];
-        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + cb * 16, v);
-        tmem_ld_wait();
-        const int col0 = iter.nt * BN + cb * 16;
-        if (sid >= 0) {
-          uint32_t o[8];
+      for (int h = 0; h < MT; ++h) {
+        const int r = h * 128 + q * 32 + lane;
+        // a warp whose 32 rows lie outside the run has nothing to store (warp-uniform test)
+        if (h * 128 + q * 32 >= row_hi || h * 128 + q * 32 + 32 <= row_lo) continue;
+        int sid = -1;
+        if (r >= row_lo && r < row_hi) {
+          const int64_t pos = (int64_t)iter.tile * (iter.blocks_per_tile * iter.bs) + r;
+          if (pos < p.num_sorted) sid = p.sorted_ids[pos];
+          if (sid < 0 || (int64_t)sid >= p.size_m * p.top_k) sid = -1;
+        }
+        const float tw = (sid >= 0 && p.mul_topk) ? p.topk_weights[sid] : 1.f;
+#pragma unroll 1
+        for (int cb = 0; cb < BN / 16; ++cb) {
+          uint32_t v[16];
+          tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + h * 256 + cb * 16, v);
+          tmem_ld_wait();
+          const int col0 = iter.nt * BN + cb * 16;
+          if (sid >= 0) {
+            uint32_t o[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float x0 = __uint_as_float(v[2 * i]) * gs, x1 = __uint_as_float(v[2 * i + 1]) * gs;
-            if (bias != nullptr) {
-              x0 += to_float<T>(bias[(int64_t)e * p.N + bias_index(col0 + 2 * i)]) * bias_mul;
-              x1 += to_float<T>(bias[(int64_t)e * p.N + bias_index(col0 + 2 * i + 1)]) * bias_mul;
+            for (int i = 0; i < 8; ++i) {
+              float x0 = __uint_as_float(v[2 * i]) * gs, x1 = __uint_as_float(v[2 * i + 1]) * gs;
+              if (bias != nullptr) {
+                x0 += to_float<T>(bias[(int64_t)e * p.N + bias_index(col0 + 2 * i)]) * bias_mul;
+                x1 += to_float<T>(bias[(int64_t)e * p.N + bias_index(col0 + 2 * i + 1)]) * bias_mul;
+              }
+              o[i] = pack_out<T>(x0 * tw, x1 * tw);
             }
-            o[i] = pack_out<T>(x0 * tw, x1 * tw);
+            uint4* dst = reinterpret_cast<uint4*>(C + (int64_t)sid * p.N + col0);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
           }
-          uint4* dst = reinterpret_cast<uint4*>(C + (int64_t)sid * p.N + col0);
-          dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-          dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
         }
       }
       tc_fence_before();
@@ -873,10 +883,10 @@ int launch_dtype(const GemmArgs& g) {
 }
 
 
-template <typename T, int FMT>
+template <typename T, int FMT, int MT>
 int launch_moe(const GemmArgs& g) {
   constexpr int BITS = format_bits(FMT);
-  using L = TcLayout<BITS, 1, MOE_A_STAGES>;
+  using L = TcLayout<BITS, MT, MT == 1 ? MOE_A_STAGES : 3>;
   constexpr int SMEM = 1024 + L::TOTAL;
   static_assert(SMEM <= 227 * 1024, "shared memory budget");
   const int64_t K = g.size_k, N = g.size_n, E = g.num_experts;
@@ -894,7 +904,7 @@ int launch_moe(const GemmArgs& g) {
   // Few routes per expert: blocks of different experts cannot share an MMA, so one block per tile
   // gives every (block, column group) its own CTA.  Many routes per expert: fill the 128 rows.
   const int64_t routes = g.size_m * g.top_k;
-  p.blocks_per_tile = (routes / E < g.block_size) ? 1 : 128 / g.block_size;
+  p.blocks_per_tile = (routes / E < g.block_size) ? 1 : (128 * MT) / g.block_size;
   p.num_sorted = (int)g.num_sorted;
   const int64_t blocks = g.num_sorted / g.block_size;
   p.num_tiles = (int)((blocks + p.blocks_per_tile - 1) / p.blocks_per_tile);
@@ -921,7 +931,7 @@ int launch_moe(const GemmArgs& g) {
     count_launches(1);
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)g.num_sorted};
     const uint64_t strides[1] = {(uint64_t)K * 2};
-    const uint32_t box[2] = {BK, 128};
+    const uint32_t box[2] = {BK, 128 * MT};
     if (int rc = encode_tensor_map(&tmA, kHalf<T> ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                                    g.scratch, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
@@ -956,27 +966,36 @@ int launch_moe(const GemmArgs& g) {
   int dev = 0;
   MB_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !attr_set[dev]) {
-    MB_CUDA(cudaFuncSetAttribute(tc_moe_kernel<T, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    MB_CUDA(cudaFuncSetAttribute(tc_moe_kernel<T, FMT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     attr_set[dev] = true;
   }
   const int64_t work = (int64_t)p.num_tiles * p.n_tiles;
   const int grid = (int)(work < sm_count() ? work : sm_count());
-  tc_moe_kernel<T, FMT><<<grid, THREADS, SMEM, g.stream>>>(tmW, tmA, tmS, tmZ, p);
+  tc_moe_kernel<T, FMT, MT><<<grid, THREADS, SMEM, g.stream>>>(tmW, tmA, tmS, tmZ, p);
   MB_CUDA(cudaGetLastError());
   count_launches(1);
   return 0;
 }
 
+template <typename T, int FMT>
+int launch_moe_mt(const GemmArgs& g) {
+  // 256-row tiles pay off once an expert's run of rows spans most of a tile: from about 192 routes per
+  // expert on average; below that the second half of a tile would mostly multiply rows of other experts.
+  const int64_t routes = g.size_m * g.top_k;
+  if (routes / g.num_experts >= 192) return launch_moe<T, FMT, 2>(g);
+  return launch_moe<T, FMT, 1>(g);
+}
+
 template <typename T>
 int launch_moe_dtype(const GemmArgs& g) {
   switch (g.format) {
-    case kU4B8: return launch_moe<T, kU4B8>(g);
-    case kU4: return launch_moe<T, kU4>(g);
-    case kU8B128: return launch_moe<T, kU8B128>(g);
-    case kU8: return launch_moe<T, kU8>(g);
-    case kFP8: return launch_moe<T, kFP8>(g);
-    case kNVFP4: return launch_moe<T, kNVFP4>(g);
-    case kMXFP4: return launch_moe<T, kMXFP4>(g);
+    case kU4B8: return launch_moe_mt<T, kU4B8>(g);
+    case kU4: return launch_moe_mt<T, kU4>(g);
+    case kU8B128: return launch_moe_mt<T, kU8B128>(g);
+    case kU8: return launch_moe_mt<T, kU8>(g);
+    case kFP8: return launch_moe_mt<T, kFP8>(g);
+    case kNVFP4: return launch_moe_mt<T, kNVFP4>(g);
+    case kMXFP4: return launch_moe_mt<T, kMXFP4>(g);
   }
   return 1;
 }
