@@ -164,7 +164,8 @@ extern "C" int marlin_b200_gemm(const void* a, void* c, const int32_t* b_q_weigh
 
 extern "C" int64_t marlin_b200_moe_gemm_scratch_bytes(int64_t num_sorted, int64_t size_n, int64_t size_k, int) {
   if (size_n % 256 != 0 || size_k % 64 != 0) return 0;  // served by the shape-agnostic kernel
-  return num_sorted * size_k * 2;
+  // the routed rows in sorted order, then the tile list (one entry per block of at least 8 routes)
+  return ((num_sorted * size_k * 2 + 255) & ~(int64_t)255) + (num_sorted / 8 + 64) * 4;
 }
 
 extern "C" int marlin_b200_moe_gemm(const void* a, void* c, const int32_t* b_q_weight,

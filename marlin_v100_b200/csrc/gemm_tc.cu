@@ -465,6 +465,8 @@ struct MoeParams {
   int num_sorted, num_experts;
   int bs, blocks_per_tile, top_k, mul_topk;
   uint32_t raw_tx;
+  const int32_t* tile_start;  // first block of every tile (written by moe_tile_list_kernel)
+  const int32_t* tile_count;  // number of tiles
 };
 
 // Copies the activation rows into the order of sorted_token_ids (row pos <- A[sid / top_k], zeros for
@@ -488,46 +490,91 @@ __global__ void __launch_bounds__(256) moe_gather_rows_kernel(const T* __restric
   }
 }
 
+// Cuts the sorted route list into tiles that never mix experts: a tile starts at the first block of an
+// expert's run and then every blocks_per_tile blocks inside the run.  One CTA of 1024 threads; blocks are
+// scanned 1024 at a time (a max-scan of run starts, then a sum-scan to compact the tile starts).
+__global__ void __launch_bounds__(1024) moe_tile_list_kernel(const int32_t* __restrict__ expert_ids,
+                                                            const int32_t* __restrict__ num_post_pad, int num_sorted,
+                                                            int bs, int blocks_per_tile, int num_experts,
+                                                            int32_t* __restrict__ tile_start,
+                                                            int32_t* __restrict__ tile_count) {
+  __shared__ int s_scan[1024];
+  __shared__ int s_carry_start, s_carry_count;
+  const int tid = threadIdx.x;
+  const int nb = min(num_post_pad[0], num_sorted) / bs;
+  if (tid == 0) { s_carry_start = 0; s_carry_count = 0; }
+  __syncthreads();
+  for (int b0 = 0; b0 < nb; b0 += 1024) {
+    const int b = b0 + tid;
+    int e = -1, run_start = -1;
+    if (b < nb) {
+      e = expert_ids[b];
+      if (b == 0 || expert_ids[b - 1] != e) run_start = b;
+    }
+    // inclusive max-scan of the run starts, seeded with the run that reaches into this batch
+    s_scan[tid] = (tid == 0 && run_start < 0) ? s_carry_start : run_start;
+    __syncthreads();
+    for (int off = 1; off < 1024; off <<= 1) {
+      const int v = (tid >= off) ? s_scan[tid - off] : -1;
+      __syncthreads();
+      s_scan[tid] = max(s_scan[tid], v);
+      __syncthreads();
+    }
+    run_start = s_scan[tid];
+    const int carry_start = s_scan[1023];
+    const bool is_start = b < nb && e >= 0 && e < num_experts && ((b - run_start) % blocks_per_tile) == 0;
+    __syncthreads();
+    s_scan[tid] = is_start ? 1 : 0;
+    __syncthreads();
+    for (int off = 1; off < 1024; off <<= 1) {
+      const int v = (tid >= off) ? s_scan[tid - off] : 0;
+      __syncthreads();
+      s_scan[tid] += v;
+      __syncthreads();
+    }
+    const int base = s_carry_count;
+    if (is_start) tile_start[base + s_scan[tid] - 1] = b;
+    const int batch_total = s_scan[1023];
+    __syncthreads();
+    if (tid == 0) { s_carry_start = carry_start; s_carry_count = base + batch_total; }
+    __syncthreads();
+  }
+  if (tid == 0) tile_count[0] = s_carry_count;
+}
+
+// Work items of a CTA: (tile, column group) pairs, tile-major, strided by the grid.
 struct ItemIter {
-  int w, total, stride, n_tiles, blocks_per_tile, bs, num_blocks, num_experts;
-  int tile, nt, blk, blk_end;
+  int w, total, stride, n_tiles, blocks_per_tile, bs, num_blocks;
+  int nt, blk;
   const int32_t* expert_ids;
+  const int32_t* tile_start;
   __device__ void init(const MoeParams& p) {
     stride = gridDim.x;
     w = (int)blockIdx.x - stride;
-    total = p.num_tiles * p.n_tiles;
+    total = p.tile_count[0] * p.n_tiles;
     n_tiles = p.n_tiles;
     blocks_per_tile = p.blocks_per_tile;
     bs = p.bs;
-    const int padded = min(p.num_post_pad[0], p.num_sorted);
-    num_blocks = padded / p.bs;
-    num_experts = p.num_experts;
+    num_blocks = min(p.num_post_pad[0], p.num_sorted) / p.bs;
     expert_ids = p.expert_ids;
-    blk = blk_end = 0;
-    tile = nt = 0;
+    tile_start = p.tile_start;
+    blk = nt = 0;
   }
-  // Advances to the next run of same-expert blocks; false when this CTA has no more work.
+  // Advances to the next item; rows [0, row_hi) of the tile that starts at block `blk` belong to expert e.
   __device__ bool next(int& e, int& row_lo, int& row_hi) {
-    for (;;) {
-      if (blk >= blk_end) {
-        w += stride;
-        if (w >= total) return false;
-        tile = w / n_tiles;
-        nt = w - tile * n_tiles;
-        blk = tile * blocks_per_tile;
-        blk_end = min(blk + blocks_per_tile, num_blocks);
-        if (blk >= blk_end) continue;
-      }
-      const int lo = blk;
-      e = expert_ids[blk];
-      ++blk;
-      while (blk < blk_end && expert_ids[blk] == e) ++blk;
-      if (e < 0 || e >= num_experts) continue;
-      row_lo = (lo - tile * blocks_per_tile) * bs;
-      row_hi = (blk - tile * blocks_per_tile) * bs;
-      return true;
-    }
+    w += stride;
+    if (w >= total) return false;
+    const int ti = w / n_tiles;
+    nt = w - ti * n_tiles;
+    blk = tile_start[ti];
+    e = expert_ids[blk];
+    int count = 1;
+    while (count < blocks_per_tile && blk + count < num_blocks && expert_ids[blk + count] == e) ++count;
+    row_lo = 0;
+    row_hi = count * bs;
+    return true;
   }
+  __device__ int row0() const { return blk * bs; }
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
@@ -623,7 +670,7 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       uint32_t ph = 0;
       bool ok = true;
       while (ok && iter.next(e, row_lo, row_hi)) {
-        const int row0 = iter.tile * (iter.blocks_per_tile * iter.bs);
+        const int row0 = iter.row0();
         for (int c = 0; c < p.kc; ++c) {
           { PROF_T0();
           if (!mbar_wait(a_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 12); ok = false; break; }
@@ -691,7 +738,7 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (h * 128 + q * 32 >= row_hi || h * 128 + q * 32 + 32 <= row_lo) continue;
         int sid = -1;
         if (r >= row_lo && r < row_hi) {
-          const int64_t pos = (int64_t)iter.tile * (iter.blocks_per_tile * iter.bs) + r;
+          const int64_t pos = (int64_t)iter.row0() + r;
           if (pos < p.num_sorted) sid = p.sorted_ids[pos];
           if (sid < 0 || (int64_t)sid >= p.size_m * p.top_k) sid = -1;
         }
@@ -901,13 +948,12 @@ int launch_moe(const GemmArgs& g) {
   p.kc = (int)((K + BK - 1) / BK);
   p.n_tiles = (int)(N / BN);
   p.bs = g.block_size;
-  // Few routes per expert: blocks of different experts cannot share an MMA, so one block per tile
-  // gives every (block, column group) its own CTA.  Many routes per expert: fill the 128 rows.
-  const int64_t routes = g.size_m * g.top_k;
-  p.blocks_per_tile = (routes / E < g.block_size) ? 1 : (128 * MT) / g.block_size;
+  // A tile holds up to 128 * MT rows of one expert (blocks of different experts cannot share an MMA);
+  // the tiles are listed on the device from expert_ids, so none of them straddles two experts.
+  p.blocks_per_tile = (128 * MT) / g.block_size;
   p.num_sorted = (int)g.num_sorted;
   const int64_t blocks = g.num_sorted / g.block_size;
-  p.num_tiles = (int)((blocks + p.blocks_per_tile - 1) / p.blocks_per_tile);
+  p.num_tiles = (int)blocks;  // upper bound; the device-side count is what the kernel walks
   p.num_experts = (int)E; p.top_k = g.top_k; p.mul_topk = g.mul_topk;
   const int srow_bytes = format_scale_is_byte(FMT) ? BN : BN * 2;
   p.raw_tx = L::RAW_W + p.rpc * srow_bytes * (format_has_zp(FMT) ? 2 : 1);
@@ -916,7 +962,8 @@ int launch_moe(const GemmArgs& g) {
   CUtensorMap tmW, tmA, tmS, tmZ;
   {
     // activation rows in sorted order live in the scratch buffer
-    const int64_t need = (int64_t)g.num_sorted * K * 2;
+    const int64_t rows_bytes = ((int64_t)g.num_sorted * K * 2 + 255) & ~(int64_t)255;
+    const int64_t need = rows_bytes + (blocks + 64) * 4;
     if (g.scratch == nullptr || g.scratch_bytes < need) {
       set_error("moe scratch buffer too small: %lld bytes given, %lld needed", (long long)g.scratch_bytes, (long long)need);
       return MARLIN_B200_ESCRATCH;
@@ -928,7 +975,14 @@ int launch_moe(const GemmArgs& g) {
                                                             g.sorted_ids, g.num_post_pad, (int)g.num_sorted, g.size_m,
                                                             g.top_k, (int)K);
     MB_CUDA(cudaGetLastError());
-    count_launches(1);
+    int32_t* tile_count = reinterpret_cast<int32_t*>(reinterpret_cast<char*>(g.scratch) + rows_bytes);
+    int32_t* tile_start = tile_count + 64;
+    moe_tile_list_kernel<<<1, 1024, 0, g.stream>>>(g.expert_ids, g.num_post_pad, (int)g.num_sorted, g.block_size,
+                                                   p.blocks_per_tile, (int)E, tile_start, tile_count);
+    MB_CUDA(cudaGetLastError());
+    p.tile_start = tile_start;
+    p.tile_count = tile_count;
+    count_launches(2);
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)g.num_sorted};
     const uint64_t strides[1] = {(uint64_t)K * 2};
     const uint32_t box[2] = {BK, 128 * MT};
