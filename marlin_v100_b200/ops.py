@@ -167,6 +167,37 @@ def marlin_gemm(a: torch.Tensor, c: torch.Tensor | None, b_q_weight: torch.Tenso
     and ``use_fp32_reduce`` are accepted and ignored, as in the reference (marlin.cu:103-106); the
     split-K scratch is allocated here from torch's caching allocator and the caller's workspace is
     never touched."""
+    c, call = _gemm_prepare(a, c, b_q_weight, b_bias, b_scales, a_scales, global_scale, b_zeros, g_idx, perm,
+                            b_q_type, size_m, size_n, size_k, is_zp_float)
+    if call is not None:
+        with torch.cuda.device(a.device):
+            call()
+    return c
+
+
+class PreparedGemm:
+    """`marlin_gemm` with its arguments checked and converted once.  Calling the object only enqueues
+    the kernels on the current stream of the tensors' device (which must be the current device), for
+    loops that run the same layer on the same buffers every step: there the argument checks of
+    `marlin_gemm` cost more host time than a decode-sized GEMM takes on the GPU.  The output tensor is
+    `.c`; the buffers passed in (and the scratch taken here) must stay alive and in place."""
+
+    def __init__(self, a, c, b_q_weight, b_bias, b_scales, global_scale, b_zeros, b_q_type, size_m, size_n,
+                 size_k, is_zp_float=False):
+        self.c, self._call = _gemm_prepare(a, c, b_q_weight, b_bias, b_scales, None, global_scale, b_zeros, None,
+                                           None, b_q_type, size_m, size_n, size_k, is_zp_float)
+        self._keep = (a, b_q_weight, b_bias, b_scales, global_scale, b_zeros)
+
+    def __call__(self) -> torch.Tensor:
+        if self._call is not None:
+            self._call()
+        return self.c
+
+
+def _gemm_prepare(a, c, b_q_weight, b_bias, b_scales, a_scales, global_scale, b_zeros, g_idx, perm, b_q_type,
+                  size_m, size_n, size_k, is_zp_float):
+    """Validation, output / scratch allocation and argument conversion of the dense GEMM.  Returns the
+    output tensor and a closure that enqueues the work (None when size_m == 0)."""
     lib = _lib.load()
     _check_act_order_absent(g_idx, perm)
     _check(a_scales is None, "a_scales can only be used for 8bit activation.")
@@ -205,7 +236,7 @@ def marlin_gemm(a: torch.Tensor, c: torch.Tensor | None, b_q_weight: torch.Tenso
         else:
             c = torch.empty((size_m, size_n), dtype=a.dtype, device=a.device)
         if size_m == 0:
-            return c
+            return c, None
 
         _check(b_scales.dim() == 2, f"b_scales rank = {b_scales.dim()} is not 2")
         _check(b_scales.size(1) == size_n, f"b_scales dim 1 = {b_scales.size(1)} is not size_n = {size_n}")
@@ -249,11 +280,15 @@ def marlin_gemm(a: torch.Tensor, c: torch.Tensor | None, b_q_weight: torch.Tenso
 
         nbytes = lib.marlin_b200_gemm_scratch_bytes(size_m, size_n, size_k, fmt)
         scratch = _scratch(nbytes, a.device)
-        _lib.check(lib.marlin_b200_gemm(
-            _ptr(a), _ptr(c), _ptr(b_q_weight), _ptr(b_scales), _ptr(b_zeros) if has_zp else None,
-            _ptr(b_bias), _ptr(global_scale), act, fmt, size_m, size_n, size_k, a.stride(0), num_groups,
-            _ptr(scratch), nbytes, _stream(a.device)))
-    return c
+        args = (_ptr(a), _ptr(c), _ptr(b_q_weight), _ptr(b_scales), _ptr(b_zeros) if has_zp else None,
+                _ptr(b_bias), _ptr(global_scale), act, fmt, size_m, size_n, size_k, a.stride(0), num_groups,
+                _ptr(scratch), nbytes)
+        device, fn = a.device, lib.marlin_b200_gemm
+
+        def call(_scratch_ref=scratch):
+            _lib.check(fn(*args, _stream(device)))
+
+    return c, call
 
 
 # --------------------------------------------------------------------------------------------

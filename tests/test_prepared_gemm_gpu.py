@@ -1,0 +1,27 @@
+"""The prepared-call form of the dense GEMM gives the same bits as the operator call."""
+import pytest
+import torch
+
+from oracle import marlin_oracle as mo
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+
+def test_prepared_gemm_matches_operator_call():
+    from marlin_v100_b200 import ops
+    a, qw = util.make_dense(16, 512, 512, "u4", torch.bfloat16, 128)
+    d = util.to_dev(qw)
+    a = a.cuda()
+    ws = torch.empty(0, dtype=torch.int32, device="cuda")
+    ref = ops.marlin_gemm(a, None, d.packed, None, d.scales, None, None, d.zeros, None, None, ws, qw.type_id,
+                          16, 512, 512, True, False, True, True)
+    plan = ops.PreparedGemm(a, None, d.packed, None, d.scales, None, d.zeros, qw.type_id, 16, 512, 512, True)
+    out1 = plan().clone()
+    a.mul_(2.0)          # same buffers, new contents: the plan reads them at call time
+    out2 = plan().clone()
+    torch.cuda.synchronize()
+    assert torch.equal(out1, ref)
+    assert mo.mean_rel_err(out2.float().cpu(), 2.0 * ref.float().cpu()) < 1e-2
+    with pytest.raises(RuntimeError):
+        ops.PreparedGemm(a, None, d.packed, None, d.scales, None, d.zeros, qw.type_id, 16, 500, 512, True)
