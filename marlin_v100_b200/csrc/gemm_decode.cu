@@ -281,6 +281,11 @@ __device__ __forceinline__ void fixup(float (&dst)[8][MB][4], const float (&src)
 
 __device__ __forceinline__ int64_t range_start(int64_t p, int64_t U, int64_t P) { return p * U / P; }
 
+// Programmatic dependent launch: the reduce kernel is allowed to become resident while the main kernel
+// still runs (its launch latency disappears); it waits here before it reads the partial sums.
+__device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   if constexpr (kIsHalf<T>) {
@@ -333,6 +338,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const int64_t U = (int64_t)p.ng * p.kc;
   const int64_t u0 = range_start(blockIdx.x, U, p.num_ctas);
   const int64_t u1 = range_start(blockIdx.x + 1, U, p.num_ctas);
+  pdl_release_dependents();
 
   if (warp == CONSUMER_WARPS) {
     // ---------------- producers ----------------
@@ -641,6 +647,7 @@ __global__ void __launch_bounds__(GROUP_N) decode_reduce_kernel(const DecodePara
   const int64_t ua = (int64_t)g * p.kc, ub = ua + p.kc - 1;
   const int64_t pa = ((ua + 1) * P - 1) / U, pb = ((ub + 1) * P - 1) / U;
   if (pa == pb) return;  // written directly by its only owner
+  pdl_wait_prior_grid();
   const int col = threadIdx.x;
   const int n = g * GROUP_N + col;
   constexpr int SLOT = MB * 8 * GROUP_N;
@@ -766,8 +773,16 @@ int launch_one(const GemmArgs& g, const void* a, void* c, int m) {
   MB_CUDA(cudaGetLastError());
   count_launches(1);
   if (U % p.num_ctas != 0 || (U / p.num_ctas) % p.kc != 0) {
-    decode_reduce_kernel<T, FMT, MB><<<dim3(p.ng, m), GROUP_N, 0, g.stream>>>(p);
-    MB_CUDA(cudaGetLastError());
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.ng, m);
+    cfg.blockDim = dim3(GROUP_N);
+    cfg.stream = g.stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MB_CUDA(cudaLaunchKernelEx(&cfg, decode_reduce_kernel<T, FMT, MB>, p));
     count_launches(1);
   }
   return 0;

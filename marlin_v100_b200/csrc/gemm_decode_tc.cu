@@ -95,6 +95,12 @@ __device__ int g_dtc_status = 0;
 
 __device__ __forceinline__ int64_t range_start(int64_t p, int64_t U, int64_t P) { return p * U / P; }
 
+// Programmatic dependent launch: the three kernels of a call are chained so that the next one may start
+// (set up barriers, stream weights) while the previous one still runs; whoever consumes the previous
+// kernel's output waits here first.
+__device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // The (group, chunk) units of a CTA in order, with the segment / scope boundaries every role needs.
 // A segment is a run of chunks of one column group, a scope a run of chunks that share a scale row.
 struct UnitWalk {
@@ -172,6 +178,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a, int64_t a_stride, int M, int K,
                                                          int8_t* __restrict__ digits, float* __restrict__ row_scale) {
   const int m = blockIdx.x, tid = threadIdx.x;
+  pdl_release_dependents();
   __shared__ float s_red[8];
   __shared__ float s_max;
   const int vecs = K / 8;
@@ -283,6 +290,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   const int64_t u1 = range_start(blockIdx.x + 1, U, p.num_ctas);
   UnitWalk w;
   w.init(u0, u1, p.kc, p.cps);
+  pdl_release_dependents();
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -292,20 +300,39 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const int total = (int)(u1 - u0);
       int g = w.g, c = w.c + lane;
       while (c >= p.kc) { c -= p.kc; ++g; }
-      for (int i = lane; i < total; i += 4) {
+      auto issue = [&](int i, int gi, int ci, bool weights, bool digits) {
+        const int s = i & (STAGES - 1);
+        const uint32_t st = base + s * STAGE_BYTES;
+        if (weights) {
+          mbar_arrive_expect_tx(full(s), p.tx_bytes);
+          tma_load_3d(st, &tmW, full(s), 0, gi * 16, ci * KT16);
+          const int srow = (p.num_groups == 1) ? 0 : (ci / p.cps);
+          tma_load_2d(st + OFF_S, &tmS, full(s), gi * GROUP_N, srow);
+          if constexpr (format_has_zp(FMT)) tma_load_2d(st + OFF_Z, &tmZ, full(s), gi * GROUP_N, srow);
+        }
+        if (digits) tma_load_2d(st + OFF_ACT, &tmA, full(s), ci * KCH, 0);
+      };
+      // First lap of the ring: weights and scales go out at once, the digit planes only after the
+      // kernel that writes them has finished (it may still be running when this kernel starts).
+      const int g0 = g, c0 = c;
+      c += 4;
+      while (c >= p.kc) { c -= p.kc; ++g; }
+      const int g1 = g, c1 = c;
+      if (lane < total) issue(lane, g0, c0, true, false);
+      if (lane + 4 < total) issue(lane + 4, g1, c1, true, false);
+      pdl_wait_prior_grid();
+      if (lane < total) issue(lane, g0, c0, false, true);
+      if (lane + 4 < total) issue(lane + 4, g1, c1, false, true);
+      c += 4;
+      while (c >= p.kc) { c -= p.kc; ++g; }
+      for (int i = lane + 8; i < total; i += 4) {
         const int s = i & (STAGES - 1);
         const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
         if (!mbar_wait(empty(s), ph ^ 1u, &s_abort) || !mbar_wait(mma_done(s), ph ^ 1u, &s_abort)) {
           atomicExch(&g_dtc_status, 1);
           break;
         }
-        const uint32_t st = base + s * STAGE_BYTES;
-        mbar_arrive_expect_tx(full(s), p.tx_bytes);
-        tma_load_3d(st, &tmW, full(s), 0, g * 16, c * KT16);
-        tma_load_2d(st + OFF_ACT, &tmA, full(s), c * KCH, 0);
-        const int srow = (p.num_groups == 1) ? 0 : (c / p.cps);
-        tma_load_2d(st + OFF_S, &tmS, full(s), g * GROUP_N, srow);
-        if constexpr (format_has_zp(FMT)) tma_load_2d(st + OFF_Z, &tmZ, full(s), g * GROUP_N, srow);
+        issue(i, g, c, true, true);
         c += 4;
         while (c >= p.kc) { c -= p.kc; ++g; }
       }
@@ -446,6 +473,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         ++j;
       }
       if (w.seg_end()) {
+        if (first_segment) pdl_wait_prior_grid();  // row factors come from the kernel in front
         if (ok && s_abort == 0) {
           const bool whole = (seg_c0 == 0) && (w.c == p.kc - 1);
           if (whole) {
@@ -546,6 +574,7 @@ __global__ void __launch_bounds__(GROUP_N) decode_tc_reduce_kernel(const DtParam
   const int64_t ua = (int64_t)g * p.kc, ub = ua + p.kc - 1;
   const int64_t pa = ((ua + 1) * P - 1) / U, pb = ((ub + 1) * P - 1) / U;
   if (pa == pb) return;  // written directly by its only owner
+  pdl_wait_prior_grid();
   const int col = threadIdx.x;
   const int n = g * GROUP_N + col;
   constexpr int SLOT = 16 * GROUP_N;
@@ -646,12 +675,28 @@ int launch_one(const GemmArgs& g, const void* a, void* c, int m) {
     MB_CUDA(cudaFuncSetAttribute(decode_tc_kernel<T, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     attr_set[dev] = true;
   }
-  decode_tc_kernel<T, FMT><<<p.num_ctas, THREADS, SMEM, g.stream>>>(tmW, tmA, tmS, tmZ, p);
-  MB_CUDA(cudaGetLastError());
-  count_launches(1);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.num_ctas);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = g.stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MB_CUDA(cudaLaunchKernelEx(&cfg, decode_tc_kernel<T, FMT>, tmW, tmA, tmS, tmZ, p));
+    count_launches(1);
+  }
   if (U % p.num_ctas != 0 || (U / p.num_ctas) % p.kc != 0) {
-    decode_tc_reduce_kernel<T><<<dim3(p.ng, m), GROUP_N, 0, g.stream>>>(p);
-    MB_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.ng, m);
+    cfg.blockDim = dim3(GROUP_N);
+    cfg.stream = g.stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MB_CUDA(cudaLaunchKernelEx(&cfg, decode_tc_reduce_kernel<T>, p));
     count_launches(1);
   }
   return 0;

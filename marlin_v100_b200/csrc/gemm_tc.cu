@@ -3,7 +3,7 @@
 //
 // One persistent CTA per SM, 768 threads, warp-specialised:
 //   warp 0      TMA producer of the packed weight chunks (+ their scale / zero-point rows)
-//   warp 1      TMA producer of the activation tiles (grouped kernel: warps 1 and 3 gather rows)
+//   warp 1      TMA producer of the activation tiles
 //   warp 2      allocates tensor memory, issues the MMAs (one thread)
 //   warps 4-7   epilogue: tcgen05.ld the accumulator, bias / nvfp4 global scale, store C
 //   warps 8-23  dequantise: packed codes (shared memory) -> K-major 128-byte-swizzled operand tile
@@ -443,12 +443,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 // ---------------------------------------------------------------------------------------------------
 // Grouped (MoE) variant
 // ---------------------------------------------------------------------------------------------------
-// Rows come from `sorted_token_ids`: blocks of `bs` routes, each block belonging to one expert.  A
-// tile is the 128 / bs consecutive blocks that fill the 128 rows of the MMA (96 rows for bs = 48);
-// inside a tile every run of blocks of the same expert is one work item: the whole K loop with that
-// expert's weights, after which the epilogue scatters only the rows of the run (C row = route id,
-// times the router weight when asked).  Activation rows are gathered with cp.async (16 bytes at a
-// time, zero-filled for padding rows) straight into the swizzled operand layout.
+// Rows come from `sorted_token_ids`: blocks of `bs` routes, each block belonging to one expert, the
+// blocks of an expert next to each other.  moe_gather_rows_kernel first copies the activation rows into
+// that order, moe_tile_list_kernel lists the tiles: up to 128 * MT / bs consecutive blocks of ONE
+// expert, starting at the expert's first block.  A work item is (tile, column group): the whole K loop
+// with that expert's weights on rows loaded by plain TMA boxes, after which the epilogue scatters the
+// rows of the tile (C row = route id, times the router weight when asked).
 struct MoeParams {
   const void* a;
   void* c;
@@ -576,13 +576,6 @@ struct ItemIter {
   }
   __device__ int row0() const { return blk * bs; }
 };
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <typename T, int FMT, int MT>
 __global__ void __launch_bounds__(THREADS, 1)
