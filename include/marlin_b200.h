@@ -90,7 +90,9 @@ int marlin_b200_awq_repack(const int32_t* b_q_weight, int32_t* out, int64_t size
  * b_bias      : NULL, or [size_n] of the activation type in the reference's permuted order.
  * global_scale: NULL, or fp32 [1] (nvfp4 only).
  * scratch     : device buffer of at least marlin_b200_gemm_scratch_bytes() bytes (may be NULL when
- *               that is 0).  Contents on entry are irrelevant; it is overwritten.
+ *               that is 0): fp32 split-K partial sums and, for the integer-MMA kernel, the 8-bit
+ *               digit planes of the activation rows.  Contents on entry are irrelevant; it is
+ *               overwritten.
  * Requires size_k % 32 == 0 and size_n % 64 == 0.  size_m == 0 is a no-op.
  * -------------------------------------------------------------------------------------------- */
 int64_t marlin_b200_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k, int format);
@@ -135,8 +137,9 @@ int marlin_b200_gemm_static_scratch(const void* a, void* c, const int32_t* b_q_w
  * num_tokens_past_padded int32 [1], read on the device; topk_weights fp32 [size_m * top_k].
  * moe_block_size in {8, 16, 32, 48, 64}.
  * -------------------------------------------------------------------------------------------- */
-/* Scratch for marlin_b200_moe_gemm: room for the activation rows copied into sorted order,
- * num_sorted * size_k * 2 bytes (0 when the shape is served by the kernel that needs none). */
+/* Scratch for marlin_b200_moe_gemm: room for the activation rows copied into sorted order
+ * (num_sorted * size_k * 2 bytes) and the list of row tiles (0 when the shape is served by the kernel
+ * that needs none). */
 int64_t marlin_b200_moe_gemm_scratch_bytes(int64_t num_sorted, int64_t size_n, int64_t size_k, int format);
 
 int marlin_b200_moe_gemm(const void* a, void* c, const int32_t* b_q_weight, const void* b_scales,
