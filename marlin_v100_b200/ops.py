@@ -171,7 +171,7 @@ def marlin_gemm(a: torch.Tensor, c: torch.Tensor | None, b_q_weight: torch.Tenso
                             b_q_type, size_m, size_n, size_k, is_zp_float)
     if call is not None:
         with torch.cuda.device(a.device):
-            call()
+            call(None)
     return c
 
 
@@ -188,10 +188,70 @@ class PreparedGemm:
                                            None, b_q_type, size_m, size_n, size_k, is_zp_float)
         self._keep = (a, b_q_weight, b_bias, b_scales, global_scale, b_zeros)
 
-    def __call__(self) -> torch.Tensor:
+    def __call__(self, stream: int | None = None) -> torch.Tensor:
+        """Enqueues the GEMM on the current stream, or on `stream` (a raw cudaStream_t handle)."""
         if self._call is not None:
-            self._call()
+            self._call(stream)
         return self.c
+
+
+class HostPipelinedGemm:
+    """Dense GEMM for callers whose activations and results live in pinned host memory (a serving loop
+    that receives rows from the host and returns rows to it).  `submit` enqueues copy-in, GEMM and
+    copy-out of one call on three streams over `depth` staging slots, so the copies of one call overlap
+    the GEMM of its neighbours; nothing synchronises with the host until `synchronize()`.
+
+    `layers` is a list of weight sets, each a dict with `packed`, `scales` and optionally `zeros`,
+    `global_scale`, `bias`; `submit(..., layer=i)` picks one."""
+
+    def __init__(self, layers, b_q_type, size_m: int, size_n: int, size_k: int, dtype: torch.dtype,
+                 device: torch.device, depth: int = 3):
+        self.depth, self._count = depth, 0
+        self.device = device
+        with torch.cuda.device(device):
+            self._in, self._run, self._out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+            self._a = [torch.empty((size_m, size_k), dtype=dtype, device=device) for _ in range(depth)]
+            self._c = [torch.empty((size_m, size_n), dtype=dtype, device=device) for _ in range(depth)]
+            self._plans = [[PreparedGemm(self._a[s], self._c[s], w["packed"], w.get("bias"), w["scales"],
+                                         w.get("global_scale"), w.get("zeros"), b_q_type, size_m, size_n, size_k,
+                                         w.get("zeros") is not None) for w in layers] for s in range(depth)]
+            self._in_done = [torch.cuda.Event() for _ in range(depth)]
+            self._run_done = [torch.cuda.Event() for _ in range(depth)]
+            self._out_done = [torch.cuda.Event() for _ in range(depth)]
+            start = torch.cuda.Event()
+            start.record()           # the staging buffers were created on the current stream
+            for st in (self._in, self._run, self._out):
+                st.wait_event(start)
+
+    def submit(self, a_host: torch.Tensor, c_host: torch.Tensor, layer: int = 0) -> None:
+        """a_host [size_m, size_k] and c_host [size_m, size_n] in pinned host memory; c_host is valid
+        after `synchronize()` (or once the event returned by `last_event()` has completed)."""
+        s = self._count % self.depth
+        reused = self._count >= self.depth
+        self._count += 1
+        if reused:
+            self._in.wait_event(self._run_done[s])   # the GEMM that read this slot's activations is done
+        with torch.cuda.stream(self._in):
+            self._a[s].copy_(a_host, non_blocking=True)
+        self._in_done[s].record(self._in)
+        self._run.wait_event(self._in_done[s])
+        if reused:
+            self._run.wait_event(self._out_done[s])  # this slot's previous result has left the device
+        self._plans[s][layer](self._run.cuda_stream)
+        self._run_done[s].record(self._run)
+        self._out.wait_event(self._run_done[s])
+        with torch.cuda.stream(self._out):
+            c_host.copy_(self._c[s], non_blocking=True)
+        self._out_done[s].record(self._out)
+
+    def join(self) -> None:
+        """Makes the current stream wait for everything submitted so far (no host synchronisation)."""
+        cur = torch.cuda.current_stream(self.device)
+        for s in range(min(self._count, self.depth)):
+            cur.wait_event(self._out_done[s])
+
+    def synchronize(self) -> None:
+        self._out.synchronize()
 
 
 def _gemm_prepare(a, c, b_q_weight, b_bias, b_scales, a_scales, global_scale, b_zeros, g_idx, perm, b_q_type,
@@ -285,8 +345,8 @@ def _gemm_prepare(a, c, b_q_weight, b_bias, b_scales, a_scales, global_scale, b_
                 _ptr(scratch), nbytes)
         device, fn = a.device, lib.marlin_b200_gemm
 
-        def call(_scratch_ref=scratch):
-            _lib.check(fn(*args, _stream(device)))
+        def call(stream=None, _scratch_ref=scratch):
+            _lib.check(fn(*args, _stream(device) if stream is None else stream))
 
     return c, call
 

@@ -25,3 +25,22 @@ def test_prepared_gemm_matches_operator_call():
     assert mo.mean_rel_err(out2.float().cpu(), 2.0 * ref.float().cpu()) < 1e-2
     with pytest.raises(RuntimeError):
         ops.PreparedGemm(a, None, d.packed, None, d.scales, None, d.zeros, qw.type_id, 16, 500, 512, True)
+
+
+def test_host_pipelined_gemm_matches_operator_call():
+    from marlin_v100_b200 import ops
+    a, qw = util.make_dense(16, 512, 512, "u4b8", torch.float16, 128)
+    d = util.to_dev(qw)
+    ws = torch.empty(0, dtype=torch.int32, device="cuda")
+    pipe = ops.HostPipelinedGemm([dict(packed=d.packed, scales=d.scales)], qw.type_id, 16, 512, 512, torch.float16,
+                                 torch.device("cuda", torch.cuda.current_device()), depth=2)
+    g = torch.Generator().manual_seed(9)
+    ins = [torch.randn(16, 512, generator=g).to(torch.float16).pin_memory() for _ in range(5)]
+    outs = [torch.empty(16, 512, dtype=torch.float16).pin_memory() for _ in range(5)]
+    for x, y in zip(ins, outs):            # more calls than slots: the slots are reused
+        pipe.submit(x, y)
+    pipe.synchronize()
+    for x, y in zip(ins, outs):
+        ref = ops.marlin_gemm(x.cuda(), None, d.packed, None, d.scales, None, None, None, None, None, ws,
+                              qw.type_id, 16, 512, 512)
+        assert torch.equal(y, ref.cpu())
