@@ -85,7 +85,8 @@ def make_dispatch_plan(topk_ids: torch.Tensor, topk_weights: torch.Tensor, exper
     else:
         recv.copy_(send)
     local_expert = (flat - dest * experts_per_rank)[order].to(torch.int32)
-    return DispatchPlan(order, send.tolist(), recv.tolist(), local_expert,
+    counts = torch.stack((send, recv)).tolist()  # the one host synchronisation of the layer: split sizes
+    return DispatchPlan(order, counts[0], counts[1], local_expert,
                         topk_weights.reshape(-1)[order].to(torch.float32))
 
 
@@ -140,8 +141,12 @@ class ExpertParallelMoE:
         token_of = torch.div(plan.order, k, rounding_mode="floor")
         send_rows = hidden.index_select(0, token_of)
         recv_rows = _all_to_all_rows(send_rows, plan.send_counts, plan.recv_counts, self.group)
-        recv_expert = _all_to_all_rows(plan.local_expert, plan.send_counts, plan.recv_counts, self.group)
-        recv_weight = _all_to_all_rows(plan.weights, plan.send_counts, plan.recv_counts, self.group)
+        # local expert id and router weight of every row travel together (two fp32 per row; ids are small
+        # integers, exact in fp32)
+        meta = torch.stack((plan.local_expert.to(torch.float32), plan.weights), dim=1)
+        recv_meta = _all_to_all_rows(meta, plan.send_counts, plan.recv_counts, self.group)
+        recv_expert = recv_meta[:, 0].to(torch.int32)
+        recv_weight = recv_meta[:, 1].contiguous()
         out_rows = self.compute(recv_rows, recv_expert, recv_weight)
         back = _all_to_all_rows(out_rows, plan.recv_counts, plan.send_counts, self.group)
         # `back` is in `order` order: put the routes back to [T, k, H] and add them up per token
