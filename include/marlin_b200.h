@@ -196,6 +196,11 @@ int marlin_b200_silu_and_mul(const void* in, void* out, int64_t rows, int64_t in
                              void* stream);
 int marlin_b200_moe_sum(const void* in, void* out, int64_t tokens, int top_k, int64_t hidden,
                         int act_dtype, void* stream);
+/* The same sum over rows picked by an index: out[t] = sum_j in[rows[t * top_k + j]] (no counterpart in
+ * the reference: the combine step of the expert-parallel layer, whose contributions come back from
+ * the all-to-all in sender order). */
+int marlin_b200_moe_sum_rows(const void* in, const int32_t* rows, void* out, int64_t tokens, int top_k,
+                             int64_t hidden, int act_dtype, void* stream);
 
 #ifdef __cplusplus
 }

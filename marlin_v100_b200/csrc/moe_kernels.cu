@@ -319,9 +319,12 @@ __global__ void __launch_bounds__(256) silu_and_mul_kernel(const T* __restrict__
   }
 }
 
+// rows == nullptr: in is [tokens, top_k, hidden].  Otherwise rows[t * top_k + j] is the row of `in` that
+// holds the contribution of route j of token t (rows of an all-to-all that came back in sender order).
 template <typename T>
 __global__ void __launch_bounds__(256) moe_sum_kernel(const T* __restrict__ in, T* __restrict__ out,
-                                                      int64_t tokens, int top_k, int64_t hidden) {
+                                                      const int32_t* __restrict__ rows, int64_t tokens, int top_k,
+                                                      int64_t hidden) {
   const int64_t vec_per_row = hidden / 8;
   const int64_t total = tokens * vec_per_row;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -329,7 +332,8 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const T* __restrict__ in, 
     const int64_t t = idx / vec_per_row, v = idx % vec_per_row;
     float acc[8] = {};
     for (int j = 0; j < top_k; ++j) {
-      const uint4 x4 = *reinterpret_cast<const uint4*>(in + (t * top_k + j) * hidden + v * 8);
+      const int64_t row = rows != nullptr ? (int64_t)rows[t * top_k + j] : t * top_k + j;
+      const uint4 x4 = *reinterpret_cast<const uint4*>(in + row * hidden + v * 8);
       const T* xp = reinterpret_cast<const T*>(&x4);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] += to_float<T>(xp[i]);
@@ -455,15 +459,20 @@ extern "C" int marlin_b200_silu_and_mul(const void* in, void* out, int64_t rows,
 
 extern "C" int marlin_b200_moe_sum(const void* in, void* out, int64_t tokens, int top_k, int64_t hidden,
                                    int act_dtype, void* stream) {
+  return marlin_b200_moe_sum_rows(in, nullptr, out, tokens, top_k, hidden, act_dtype, stream);
+}
+
+extern "C" int marlin_b200_moe_sum_rows(const void* in, const int32_t* rows, void* out, int64_t tokens, int top_k,
+                                        int64_t hidden, int act_dtype, void* stream) {
   MB_CHECK(hidden % 8 == 0, "moe_sum needs the hidden size to be a multiple of 8, got %lld",
            (long long)hidden);
   if (tokens == 0 || hidden == 0) return 0;
   auto s = (cudaStream_t)stream;
   const int grid = grid_for(tokens * hidden / 8, 256);
   if (act_dtype == MARLIN_B200_F16)
-    moe_sum_kernel<__half><<<grid, 256, 0, s>>>((const __half*)in, (__half*)out, tokens, top_k, hidden);
+    moe_sum_kernel<__half><<<grid, 256, 0, s>>>((const __half*)in, (__half*)out, rows, tokens, top_k, hidden);
   else
-    moe_sum_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out,
+    moe_sum_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows,
                                                        tokens, top_k, hidden);
   MB_CUDA(cudaGetLastError());
   count_launches(1);

@@ -541,3 +541,17 @@ def moe_sum(input: torch.Tensor, output: torch.Tensor) -> None:
     with torch.cuda.device(input.device):
         _lib.check(lib.marlin_b200_moe_sum(_ptr(input), _ptr(output), tokens, top_k, hidden,
                                            _act_code(input.dtype), _stream(input.device)))
+
+
+def moe_sum_rows(input: torch.Tensor, rows: torch.Tensor, output: torch.Tensor) -> None:
+    """output[t] = sum_j input[rows[t, j]] for input [R, hidden], rows int32 [tokens, top_k]: the top-k
+    sum over contributions that sit in another order (the expert-parallel combine)."""
+    lib = _lib.load()
+    _check(input.is_cuda and input.is_contiguous() and output.is_contiguous() and rows.is_contiguous(),
+           "moe_sum_rows needs contiguous GPU tensors")
+    _check(rows.dtype == torch.int32, "rows must be int32")
+    tokens, top_k = rows.shape
+    hidden = input.shape[1]
+    with torch.cuda.device(input.device):
+        _lib.check(lib.marlin_b200_moe_sum_rows(_ptr(input), _ptr(rows), _ptr(output), tokens, top_k, hidden,
+                                                _act_code(input.dtype), _stream(input.device)))

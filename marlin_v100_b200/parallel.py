@@ -149,16 +149,16 @@ class ExpertParallelMoE:
         recv_weight = recv_meta[:, 1].contiguous()
         out_rows = self.compute(recv_rows, recv_expert, recv_weight)
         back = _all_to_all_rows(out_rows, plan.recv_counts, plan.send_counts, self.group)
-        # `back` is in `order` order: put the routes back to [T, k, H] and add them up per token
-        contrib = torch.empty((t * k, h), dtype=back.dtype, device=back.device)
-        contrib.index_copy_(0, plan.order, back)
-        return self._sum_routes(contrib.view(t, k, h), hidden)
+        # `back` is in `order` order: row inv[t * k + j] of it is the contribution of route j of token t
+        inv = torch.empty_like(plan.order)
+        inv[plan.order] = torch.arange(t * k, device=plan.order.device, dtype=plan.order.dtype)
+        return self._sum_routes(back, inv.view(t, k), hidden)
 
     @staticmethod
-    def _sum_routes(contrib: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
-        if contrib.is_cuda:
+    def _sum_routes(back: torch.Tensor, inv: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
+        if back.is_cuda:
             from . import ops
             out = torch.empty_like(like)
-            ops.moe_sum(contrib.contiguous(), out)
+            ops.moe_sum_rows(back.contiguous(), inv.to(torch.int32).contiguous(), out)
             return out
-        return contrib.float().sum(dim=1).to(like.dtype)
+        return back.float()[inv.reshape(-1)].view(inv.shape[0], inv.shape[1], -1).sum(dim=1).to(like.dtype)
