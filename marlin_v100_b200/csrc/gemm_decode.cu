@@ -673,34 +673,6 @@ __global__ void __launch_bounds__(GROUP_N) decode_reduce_kernel(const DecodePara
 // ---------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------
-struct MapKey {
-  const void* ptr;
-  int64_t a, b, c;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && a == o.a && b == o.b && c == o.c; }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.ptr) ^ (std::hash<int64_t>()(k.a) * 31) ^ (std::hash<int64_t>()(k.b) * 131) ^
-           (std::hash<int64_t>()(k.c) * 977);
-  }
-};
-std::mutex g_map_mutex;
-std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
-
-int cached_map(CUtensorMap* out, const MapKey& key, CUtensorMapDataType dt, int rank, const void* base,
-               const uint64_t* dims, const uint64_t* strides, const uint32_t* box, CUtensorMapSwizzle sw) {
-  std::lock_guard<std::mutex> lock(g_map_mutex);
-  auto it = g_map_cache.find(key);
-  if (it != g_map_cache.end()) {
-    *out = it->second;
-    return 0;
-  }
-  if (int rc = encode_tensor_map(out, dt, rank, base, dims, strides, box, sw)) return rc;
-  if (g_map_cache.size() > 4096) g_map_cache.clear();
-  g_map_cache.emplace(key, *out);
-  return 0;
-}
-
 template <typename T, int FMT, int MB, int SCOPE>
 int launch_one(const GemmArgs& g, const void* a, void* c, int m) {
   constexpr int BITS = format_bits(FMT);
@@ -733,7 +705,7 @@ int launch_one(const GemmArgs& g, const void* a, void* c, int m) {
     const uint64_t dims[3] = {32, (uint64_t)rows_per_kt, (uint64_t)(K / 16)};
     const uint64_t strides[2] = {128, (uint64_t)rows_per_kt * 128};
     const uint32_t box[3] = {32, (uint32_t)(BITS == 4 ? 16 : 32), KT_PER_CHUNK};
-    if (int rc = cached_map(&tmW, MapKey{g.bq, N, K, BITS}, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.bq, dims, strides,
+    if (int rc = cached_tensor_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.bq, dims, strides,
                             box, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   }
@@ -751,12 +723,12 @@ int launch_one(const GemmArgs& g, const void* a, void* c, int m) {
     const uint64_t strides[1] = {(uint64_t)N * (byte_scale ? 1 : 2)};
     const uint32_t box[2] = {GROUP_N, (uint32_t)p.rpc};
     const CUtensorMapDataType dt = byte_scale ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
-    if (int rc = cached_map(&tmS, MapKey{g.scales, N, g.num_groups, p.rpc * 16 + byte_scale}, dt, 2, g.scales, dims,
+    if (int rc = cached_tensor_map(&tmS, dt, 2, g.scales, dims,
                             strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
     tmZ = tmS;
     if (format_has_zp(FMT)) {
-      if (int rc = cached_map(&tmZ, MapKey{g.zeros, N, g.num_groups, p.rpc * 16 + byte_scale}, dt, 2, g.zeros, dims,
+      if (int rc = cached_tensor_map(&tmZ, dt, 2, g.zeros, dims,
                               strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
         return rc;
     }

@@ -152,14 +152,10 @@ __device__ __forceinline__ void tc_mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, u
       : "memory");
 }
 
-// Position, inside its block of 32, at which the digit of k is stored: the eight k of a dequant
-// thread (t = k % 32 / 8) are rotated by i ^ 2t so that the thread's shared-memory reads of the
-// packed words fall into 32 different banks.  Weights and digits use the same order, which is all a
-// contraction needs.
-__host__ __device__ __forceinline__ int digit_pos(int k) {
-  const int t = (k >> 3) & 3, i = k & 7;
-  return (k & ~31) + 8 * t + (i ^ (2 * t));
-}
+// Order of k inside a block of 32: the digit (and the weight byte) of k sits at position
+// 8t + (i ^ 2t) with t = k % 32 / 8, i = k % 8.  The eight k of a dequant thread are rotated that way so
+// that its shared-memory reads of the packed words fall into 32 different banks; weights and digits use
+// the same order, which is all a contraction needs.
 
 // Weight column (inside the 256-column group) held by lane `lane` of quadrant `quad`, tile `tile`.
 // The dequant thread (g, t) of that quadrant reads the packed words (nv = 2 quad + g / 4, sub = g % 4);
@@ -592,19 +588,6 @@ __global__ void __launch_bounds__(GROUP_N) decode_tc_reduce_kernel(const DtParam
 // ---------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------
-struct MapKey {
-  const void* ptr;
-  int64_t a, b;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && a == o.a && b == o.b; }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.ptr) ^ (std::hash<int64_t>()(k.a) * 31) ^ (std::hash<int64_t>()(k.b) * 131);
-  }
-};
-std::mutex g_map_mutex;
-std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
-
 template <typename T, int FMT>
 int launch_one(const GemmArgs& g, const void* a, void* c, int m) {
   const int64_t K = g.size_k, N = g.size_n;
@@ -633,32 +616,23 @@ int launch_one(const GemmArgs& g, const void* a, void* c, int m) {
     const uint64_t dims[2] = {(uint64_t)N, (uint64_t)g.num_groups};
     const uint64_t strides[1] = {(uint64_t)N * 2};
     const uint32_t box[2] = {GROUP_N, 1};
-    if (int rc = encode_tensor_map(&tmS, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, g.scales, dims, strides, box,
+    if (int rc = cached_tensor_map(&tmS, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, g.scales, dims, strides, box,
                                    CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
     tmZ = tmS;
     if (format_has_zp(FMT)) {
-      if (int rc = encode_tensor_map(&tmZ, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, g.zeros, dims, strides, box,
+      if (int rc = cached_tensor_map(&tmZ, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, g.zeros, dims, strides, box,
                                      CU_TENSOR_MAP_SWIZZLE_NONE))
         return rc;
     }
   }
   {
-    std::lock_guard<std::mutex> lock(g_map_mutex);
-    const MapKey key{g.bq, N, K};
-    auto it = g_map_cache.find(key);
-    if (it != g_map_cache.end()) {
-      tmW = it->second;
-    } else {
-      const uint64_t dims[3] = {32, (uint64_t)(16 * p.ng), (uint64_t)(K / 16)};
-      const uint64_t strides[2] = {128, (uint64_t)(16 * p.ng) * 128};
-      const uint32_t box[3] = {32, 16, KT16};
-      if (int rc = encode_tensor_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.bq, dims, strides, box,
-                                     CU_TENSOR_MAP_SWIZZLE_128B))
-        return rc;
-      if (g_map_cache.size() > 4096) g_map_cache.clear();
-      g_map_cache.emplace(key, tmW);
-    }
+    const uint64_t dims[3] = {32, (uint64_t)(16 * p.ng), (uint64_t)(K / 16)};
+    const uint64_t strides[2] = {128, (uint64_t)(16 * p.ng) * 128};
+    const uint32_t box[3] = {32, 16, KT16};
+    if (int rc = cached_tensor_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.bq, dims, strides, box,
+                                   CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
   }
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)NCOL};

@@ -805,34 +805,6 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 // ---------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------
-struct MapKey {
-  const void* ptr;
-  int64_t a, b, c;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && a == o.a && b == o.b && c == o.c; }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.ptr) ^ (std::hash<int64_t>()(k.a) * 31) ^ (std::hash<int64_t>()(k.b) * 131) ^
-           (std::hash<int64_t>()(k.c) * 977);
-  }
-};
-std::mutex g_map_mutex;
-std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
-
-int cached_map(CUtensorMap* out, const MapKey& key, CUtensorMapDataType dt, int rank, const void* base,
-               const uint64_t* dims, const uint64_t* strides, const uint32_t* box, CUtensorMapSwizzle sw) {
-  std::lock_guard<std::mutex> lock(g_map_mutex);
-  auto it = g_map_cache.find(key);
-  if (it != g_map_cache.end()) {
-    *out = it->second;
-    return 0;
-  }
-  if (int rc = encode_tensor_map(out, dt, rank, base, dims, strides, box, sw)) return rc;
-  if (g_map_cache.size() > 4096) g_map_cache.clear();
-  g_map_cache.emplace(key, *out);
-  return 0;
-}
-
 template <typename T, int FMT, int MT>
 int launch_tc(const GemmArgs& g) {
   constexpr int BITS = format_bits(FMT);
@@ -859,7 +831,7 @@ int launch_tc(const GemmArgs& g) {
     const uint64_t dims[3] = {32, (uint64_t)rows_per_kt, (uint64_t)(K / 16)};
     const uint64_t strides[2] = {128, (uint64_t)rows_per_kt * 128};
     const uint32_t box[3] = {32, (uint32_t)(BITS == 4 ? 16 : 32), KT};
-    if (int rc = cached_map(&tmW, MapKey{g.bq, N, K, BITS}, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.bq, dims, strides, box,
+    if (int rc = cached_tensor_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.bq, dims, strides, box,
                             CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   }
@@ -877,12 +849,12 @@ int launch_tc(const GemmArgs& g) {
     const uint64_t strides[1] = {(uint64_t)N * (byte_scale ? 1 : 2)};
     const uint32_t box[2] = {BN, (uint32_t)p.rpc};
     const CUtensorMapDataType dt = byte_scale ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
-    if (int rc = cached_map(&tmS, MapKey{g.scales, N, g.num_groups, p.rpc * 16 + byte_scale}, dt, 2, g.scales, dims,
+    if (int rc = cached_tensor_map(&tmS, dt, 2, g.scales, dims,
                             strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
     tmZ = tmS;
     if (format_has_zp(FMT)) {
-      if (int rc = cached_map(&tmZ, MapKey{g.zeros, N, g.num_groups, p.rpc * 16 + byte_scale}, dt, 2, g.zeros, dims,
+      if (int rc = cached_tensor_map(&tmZ, dt, 2, g.zeros, dims,
                               strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
         return rc;
     }
@@ -988,7 +960,7 @@ int launch_moe(const GemmArgs& g) {
     const uint64_t dims[3] = {32, (uint64_t)rows_per_kt, (uint64_t)(K / 16) * (uint64_t)E};
     const uint64_t strides[2] = {128, (uint64_t)rows_per_kt * 128};
     const uint32_t box[3] = {32, (uint32_t)(BITS == 4 ? 16 : 32), KT};
-    if (int rc = cached_map(&tmW, MapKey{g.bq, N, K, BITS + 16 * E}, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.bq, dims, strides,
+    if (int rc = cached_tensor_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.bq, dims, strides,
                             box, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   }
@@ -999,12 +971,12 @@ int launch_moe(const GemmArgs& g) {
     const uint64_t strides[1] = {(uint64_t)N * es};
     const uint32_t box[2] = {BN, (uint32_t)p.rpc};
     const CUtensorMapDataType dt = byte_scale ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
-    if (int rc = cached_map(&tmS, MapKey{g.scales, N, g.num_groups, p.rpc * 16 + byte_scale + 1024 * E}, dt, 2, g.scales,
+    if (int rc = cached_tensor_map(&tmS, dt, 2, g.scales,
                             dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
     tmZ = tmS;
     if (format_has_zp(FMT)) {
-      if (int rc = cached_map(&tmZ, MapKey{g.zeros, N, g.num_groups, p.rpc * 16 + byte_scale + 1024 * E}, dt, 2, g.zeros,
+      if (int rc = cached_tensor_map(&tmZ, dt, 2, g.zeros,
                               dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
         return rc;
     }

@@ -15,6 +15,12 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, con
                       const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
                       CUtensorMapSwizzle swizzle);
 
+// Same, through a process-wide cache keyed by (base pointer, element type, rank, dims, strides, box,
+// swizzle): encoding a map costs a few microseconds of host time, weights and scales are encoded once.
+int cached_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const void* base,
+                      const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
+                      CUtensorMapSwizzle swizzle);
+
 #ifdef __CUDACC__
 // ---- device --------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -1,6 +1,8 @@
 // Host-side tensor-map encoding.  The driver entry point is resolved through the runtime, so the
 // library carries no link-time dependency on libcuda.
+#include <array>
 #include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 #include "tma.cuh"
@@ -46,6 +48,44 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, con
               rank > 1 ? box[1] : 0);
     return MARLIN_B200_ECUDA;
   }
+  return 0;
+}
+
+namespace {
+struct MapKey {
+  const void* ptr;
+  std::array<uint64_t, 16> v;  // dtype, rank, swizzle, dims[5], strides[4], box[4] (rank <= 4 in this library)
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && v == o.v; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.ptr);
+    for (uint64_t x : k.v) h = h * 1000003u ^ std::hash<uint64_t>()(x);
+    return h;
+  }
+};
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+}  // namespace
+
+int cached_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const void* base,
+                      const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
+                      CUtensorMapSwizzle swizzle) {
+  if (rank > 4) return encode_tensor_map(map, dtype, rank, base, dims, strides, box, swizzle);
+  MapKey key{};
+  key.ptr = base;
+  key.v[0] = (uint64_t)dtype; key.v[1] = (uint64_t)rank; key.v[2] = (uint64_t)swizzle;
+  for (int i = 0; i < rank; ++i) { key.v[3 + i] = dims[i]; key.v[12 + i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) key.v[8 + i] = strides[i];
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  auto it = g_map_cache.find(key);
+  if (it != g_map_cache.end()) {
+    *map = it->second;
+    return 0;
+  }
+  if (int rc = encode_tensor_map(map, dtype, rank, base, dims, strides, box, swizzle)) return rc;
+  if (g_map_cache.size() > 4096) g_map_cache.clear();
+  g_map_cache.emplace(key, *map);
   return 0;
 }
 
