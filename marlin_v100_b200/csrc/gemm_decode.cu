@@ -404,6 +404,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 #pragma unroll
   for (int mb = 0; mb < MB; ++mb) aoff[mb] = L::OFF_A + (mb * 8 + gid) * 128 + t * 4;
 
+  // k-tiles that share a row of block scales, minus one (group 16: 0, group 32: 1, >= 64: the whole chunk)
+  const int pre_mask = min(max(p.group_size / 16, 1), KT_PER_CHUNK) - 1;
   float acc[8][MB][4];
   float tmp[(POST && SCOPE > 0) ? 8 : 1][MB][4];
   float asum[MB][4];
@@ -443,6 +445,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       const uint8_t* stp = smem + stage * L::BYTES;
       if (alive) {
         constexpr int NW = (BITS == 4) ? 4 : 8;
+        uint32_t sc[POST ? 1 : 8][2];  // decoded block scales of the thread's eight column pairs (fp4 formats)
 #pragma unroll
         for (int kt = 0; kt < KT_PER_CHUNK; ++kt) {
           uint2 xk[NW];
@@ -460,13 +463,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           const bool scope_first = (kt % SC) == 0;
           const bool scope_last = (kt % SC) == SC - 1;
 
-          // ---- scales for the multiply-before path ----
-          uint32_t sc[POST ? 1 : 8][2];
+          // ---- scales for the multiply-before path: decoded once per scale group ----
           if constexpr (!POST) {
-            const int srow_local = (p.rpc == 1) ? 0 : (kt * 16) / p.group_size;
-            const uint32_t srow = st + L::OFF_S + srow_local * SROW_BYTES;
+            if (FMT == kNVFP4 || (kt & pre_mask) == 0) {  // nvfp4: a row of scales per k-tile
+              const int srow_local = (p.rpc == 1) ? 0 : (kt * 16) / p.group_size;
+              const uint32_t srow = st + L::OFF_S + srow_local * SROW_BYTES;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) load_pre_scales<T, FMT>(srow, slot_col<BITS>(q, p_lane, gid), sc[q]);
+              for (int q = 0; q < 8; ++q) load_pre_scales<T, FMT>(srow, slot_col<BITS>(q, p_lane, gid), sc[q]);
+            }
           }
 
           // ---- weights ----
