@@ -26,7 +26,6 @@
 // partial sums to scratch, and a second small kernel adds the partials of each split group in a
 // fixed order (deterministic) and applies the epilogue (nvfp4 global scale, bias).
 #include <mutex>
-#include <unordered_map>
 
 #include "common.cuh"
 #include "tma.cuh"

@@ -32,10 +32,6 @@
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag, the kernel drains, frees
 // its tensor memory and reports through g_dtc_status.
 
-
-#include <mutex>
-#include <unordered_map>
-
 #include "codes.cuh"
 #include "common.cuh"
 #include "tcgen05.cuh"

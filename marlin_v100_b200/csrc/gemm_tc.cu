@@ -21,8 +21,6 @@
 //
 // Compiling with -DMB_TC_PROFILE adds per-role wait-cycle counters for CTA 0 and a debug entry point
 // that reads them; release builds carry neither.
-#include <mutex>
-#include <unordered_map>
 
 #include "codes.cuh"
 #include "common.cuh"
