@@ -19,7 +19,6 @@ with a plain PyTorch stand-in; on GPUs the default is the CUDA library.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Callable
 
 import torch
@@ -63,13 +62,32 @@ class ColumnParallelMarlinLinear:
 # MoE: expert parallel dispatch / combine
 # --------------------------------------------------------------------------------------------------
 
-@dataclass
 class DispatchPlan:
-    order: torch.Tensor          # [T*k] route indices sorted by destination rank (stable)
-    send_counts: list[int]       # rows sent to each rank
-    recv_counts: list[int]       # rows received from each rank
-    local_expert: torch.Tensor   # [T*k] expert id inside the destination rank, in `order` order
-    weights: torch.Tensor        # [T*k] router weight, in `order` order
+    """Routes of this rank sorted by the rank that owns their expert.  The row counts per destination are
+    exchanged with an asynchronous all-to-all that is started first; `send_counts` / `recv_counts` (the
+    one host synchronisation of the layer) are only resolved when they are first read, so the caller can
+    put more device work (the row gather) in front of that synchronisation."""
+
+    def __init__(self, order, local_expert, weights, send, recv, work):
+        self.order = order                # [T*k] route indices sorted by destination rank (stable)
+        self.local_expert = local_expert  # [T*k] expert id inside the destination rank, in `order` order
+        self.weights = weights            # [T*k] router weight, in `order` order
+        self._send, self._recv, self._work, self._counts = send, recv, work, None
+
+    def _resolve(self):
+        if self._counts is None:
+            if self._work is not None:
+                self._work.wait()
+            self._counts = torch.stack((self._send, self._recv)).tolist()
+        return self._counts
+
+    @property
+    def send_counts(self) -> list[int]:   # rows sent to each rank
+        return self._resolve()[0]
+
+    @property
+    def recv_counts(self) -> list[int]:   # rows received from each rank
+        return self._resolve()[1]
 
 
 def make_dispatch_plan(topk_ids: torch.Tensor, topk_weights: torch.Tensor, experts_per_rank: int, world: int,
@@ -77,17 +95,16 @@ def make_dispatch_plan(topk_ids: torch.Tensor, topk_weights: torch.Tensor, exper
     """Sorts the (token, route) pairs by the rank that owns their expert and exchanges the counts."""
     flat = topk_ids.reshape(-1).to(torch.int64)
     dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
-    order = torch.sort(dest, stable=True).indices
     send = torch.bincount(dest, minlength=world)[:world]
     recv = torch.empty_like(send)
+    work = None
     if world > 1:
-        dist.all_to_all_single(recv, send, group=group)
+        work = dist.all_to_all_single(recv, send, group=group, async_op=True)
     else:
         recv.copy_(send)
+    order = torch.sort(dest, stable=True).indices
     local_expert = (flat - dest * experts_per_rank)[order].to(torch.int32)
-    counts = torch.stack((send, recv)).tolist()  # the one host synchronisation of the layer: split sizes
-    return DispatchPlan(order, counts[0], counts[1], local_expert,
-                        topk_weights.reshape(-1)[order].to(torch.float32))
+    return DispatchPlan(order, local_expert, topk_weights.reshape(-1)[order].to(torch.float32), send, recv, work)
 
 
 def _all_to_all_rows(rows: torch.Tensor, send_counts: list[int], recv_counts: list[int], group) -> torch.Tensor:
@@ -138,20 +155,21 @@ class ExpertParallelMoE:
         t, h = hidden.shape
         k = topk_ids.shape[1]
         plan = make_dispatch_plan(topk_ids, topk_weights, self.experts_per_rank, self.world, self.group)
+        # everything that does not need the split sizes goes in front of the plan's host synchronisation
         token_of = torch.div(plan.order, k, rounding_mode="floor")
         send_rows = hidden.index_select(0, token_of)
-        recv_rows = _all_to_all_rows(send_rows, plan.send_counts, plan.recv_counts, self.group)
         # local expert id and router weight of every row travel together (two fp32 per row; ids are small
         # integers, exact in fp32)
         meta = torch.stack((plan.local_expert.to(torch.float32), plan.weights), dim=1)
+        # the contributions come back in `order` order: row inv[t * k + j] is route j of token t
+        inv = torch.empty_like(plan.order)
+        inv[plan.order] = torch.arange(t * k, device=plan.order.device, dtype=plan.order.dtype)
+        recv_rows = _all_to_all_rows(send_rows, plan.send_counts, plan.recv_counts, self.group)
         recv_meta = _all_to_all_rows(meta, plan.send_counts, plan.recv_counts, self.group)
         recv_expert = recv_meta[:, 0].to(torch.int32)
         recv_weight = recv_meta[:, 1].contiguous()
         out_rows = self.compute(recv_rows, recv_expert, recv_weight)
         back = _all_to_all_rows(out_rows, plan.recv_counts, plan.send_counts, self.group)
-        # `back` is in `order` order: row inv[t * k + j] of it is the contribution of route j of token t
-        inv = torch.empty_like(plan.order)
-        inv[plan.order] = torch.arange(t * k, device=plan.order.device, dtype=plan.order.dtype)
         return self._sum_routes(back, inv.view(t, k), hidden)
 
     @staticmethod
