@@ -54,6 +54,12 @@ const char* marlin_b200_version(void);
 /* Number of kernels this library has launched in this process so far (all entry points, all
  * threads).  Diagnostics only; it has no counterpart in the reference. */
 int64_t marlin_b200_launch_count(void);
+/* Diagnostic (no reference counterpart): every wait inside the pipelined kernels is bounded (about two
+ * seconds); a kernel whose wait gave up drains without touching its output and leaves a code here.
+ * *status = 0 when no kernel on the current device gave up since the last reset; otherwise byte 0 /
+ * 1 / 2 hold the code of the register-fragment decode kernel / the tensor-memory kernels / the
+ * integer-MMA decode kernel.  Synchronises with the device: call it outside the hot path. */
+int marlin_b200_kernel_status(int* status, int reset);
 
 /* Maps (b_type_id, scale kind) to a MARLIN_B200_FMT_* value, or -1.
  * Stands in for the b_type routing of csrc/quantization/marlin/marlin.cu:142-183,385-505. */

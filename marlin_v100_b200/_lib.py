@@ -18,6 +18,7 @@ SIGNATURES = {
     "marlin_b200_last_error": (_c.c_char_p, []),
     "marlin_b200_version": (_c.c_char_p, []),
     "marlin_b200_launch_count": (_i64, []),
+    "marlin_b200_kernel_status": (_int, [_vp, _int]),
     "marlin_b200_format_from_type_id": (_int, [_i64, _int]),
     "marlin_b200_gptq_repack": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp]),
     "marlin_b200_awq_repack": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),

@@ -126,6 +126,16 @@ extern "C" const char* marlin_b200_last_error(void) { return g_error; }
 extern "C" const char* marlin_b200_version(void) { return "0.1"; }
 extern "C" int64_t marlin_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+extern "C" int marlin_b200_kernel_status(int* status, int reset) {
+  MB_CHECK(status != nullptr, "null status pointer");
+  int a = 0, b = 0, c = 0;
+  if (int rc = read_decode_status(&a, reset != 0)) return rc;
+  if (int rc = read_tc_status(&b, reset != 0)) return rc;
+  if (int rc = read_decode_tc_status(&c, reset != 0)) return rc;
+  *status = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16);
+  return 0;
+}
+
 extern "C" int marlin_b200_format_from_type_id(int64_t id, int scale_kind) {
   if (id == kIdU4B8) return kU4B8;
   if (id == kIdU4) return kU4;

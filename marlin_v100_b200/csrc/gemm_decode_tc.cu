@@ -712,5 +712,16 @@ int launch_gemm_decode_tc(const GemmArgs& g) {
   return launch_dtype<__nv_bfloat16>(g);
 }
 
+// Reads (and optionally clears) the word a kernel of this file sets when one of its bounded waits gave up.
+int read_decode_tc_status(int* value, bool reset) {
+  MB_CUDA(cudaMemcpyFromSymbol(value, g_dtc_status, sizeof(int)));
+  if (reset && *value != 0) {
+    const int zero = 0;
+    MB_CUDA(cudaMemcpyToSymbol(g_dtc_status, &zero, sizeof(int)));
+  }
+  return 0;
+}
+
+
 }  // namespace mb200
 

@@ -1040,6 +1040,17 @@ int launch_gemm_tc(const GemmArgs& g) {
   return launch_dtype<__nv_bfloat16>(g);
 }
 
+// Reads (and optionally clears) the word a kernel of this file sets when one of its bounded waits gave up.
+int read_tc_status(int* value, bool reset) {
+  MB_CUDA(cudaMemcpyFromSymbol(value, g_tc_status, sizeof(int)));
+  if (reset && *value != 0) {
+    const int zero = 0;
+    MB_CUDA(cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int)));
+  }
+  return 0;
+}
+
+
 }  // namespace mb200
 
 #ifdef MB_TC_PROFILE

@@ -555,3 +555,13 @@ def moe_sum_rows(input: torch.Tensor, rows: torch.Tensor, output: torch.Tensor) 
     with torch.cuda.device(input.device):
         _lib.check(lib.marlin_b200_moe_sum_rows(_ptr(input), _ptr(rows), _ptr(output), tokens, top_k, hidden,
                                                 _act_code(input.dtype), _stream(input.device)))
+
+
+def kernel_status(reset: bool = False) -> int:
+    """0 when no pipelined kernel on the current device gave up on one of its bounded waits since the
+    last reset (see marlin_b200_kernel_status); synchronises with the device."""
+    import ctypes
+    lib = _lib.load()
+    value = ctypes.c_int(0)
+    _lib.check(lib.marlin_b200_kernel_status(ctypes.byref(value), int(reset)))
+    return int(value.value)
