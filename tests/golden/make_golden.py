@@ -29,7 +29,9 @@ def _np(t: torch.Tensor) -> np.ndarray:
 
 
 def main() -> None:
-    ref_root = os.environ.get("REFERENCE_ROOT", "/root/reference")
+    ref_root = os.environ.get("REFERENCE_ROOT")
+    if not ref_root or not os.path.isdir(ref_root):
+        raise SystemExit("set REFERENCE_ROOT to a checkout of the reference project (its tests/ helpers are imported)")
     sys.path.insert(0, ref_root)
     from tests import helpers, quant_utils  # noqa: E402  (reference modules)
 
