@@ -151,7 +151,9 @@ extern "C" int marlin_b200_format_from_type_id(int64_t id, int scale_kind) {
 
 extern "C" int64_t marlin_b200_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k,
                                                   int format) {
-  return gemm_decode_scratch_bytes(size_m, size_n, size_k, format);
+  const int64_t a = gemm_decode_scratch_bytes(size_m, size_n, size_k, format);
+  const int64_t b = gemm_tc_scratch_bytes(size_m, size_n, size_k);
+  return a > b ? a : b;
 }
 
 extern "C" int marlin_b200_gemm(const void* a, void* c, const int32_t* b_q_weight, const void* b_scales,

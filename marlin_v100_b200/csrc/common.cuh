@@ -165,6 +165,7 @@ int launch_gemm_decode(const GemmArgs& g);          // returns 1 if the shape is
 int64_t gemm_decode_scratch_bytes(int64_t m, int64_t n, int64_t k, int format);
 int launch_gemm_decode_tc(const GemmArgs& g);       // returns 1 if the shape is not handled
 int launch_gemm_tc(const GemmArgs& g);              // returns 1 if the shape is not handled
+int64_t gemm_tc_scratch_bytes(int64_t m, int64_t n, int64_t k);
 // give-up words of the three pipelined kernel families (0 = every wait completed)
 int read_decode_status(int* value, bool reset);
 int read_tc_status(int* value, bool reset);

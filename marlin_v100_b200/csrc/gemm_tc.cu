@@ -69,9 +69,24 @@ struct TcParams {
   int kc;       // chunks along K
   int m_tiles, n_tiles;
   uint32_t raw_tx, a_tx;
+  int splits;        // k slices per tile; > 1: fp32 partials [slice][M][N], summed by tc_splitk_reduce_kernel
+  float* partials;
 };
 
 __device__ int g_tc_status = 0;
+
+// A work item of the dense kernel: (tile, k slice), the slice's chunks [c0, c1).
+struct TcItem {
+  int mt, nt, slice, c0, c1;
+  __device__ TcItem(int item, const TcParams& p) {
+    const int tile = item / p.splits;
+    slice = item - tile * p.splits;
+    mt = tile % p.m_tiles;
+    nt = tile / p.m_tiles;
+    c0 = (int)((int64_t)p.kc * slice / p.splits);
+    c1 = (int)((int64_t)p.kc * (slice + 1) / p.splits);
+  }
+};
 
 #ifdef MB_TC_PROFILE
 // Per-role wait-cycle counters of CTA 0 (debug builds only): [role][slot]
@@ -283,7 +298,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
-  const int num_tiles = p.m_tiles * p.n_tiles;
+  const int num_items = p.m_tiles * p.n_tiles * p.splits;
   constexpr int ROWS_PER_KT = (BITS == 4) ? 16 : 32;
 
   if (warp == 0) {
@@ -292,9 +307,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int nt = tile / p.m_tiles;
-        for (int c = 0; c < p.kc; ++c) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const TcItem it(item, p);
+        const int nt = it.nt;
+        for (int c = it.c0; c < it.c1; ++c) {
           if (!mbar_wait(raw_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 1); ok = false; break; }
           const uint32_t st = base + L::OFF_RAW + s * L::RAW_BYTES;
           mbar_arrive_expect_tx(raw_full(s), p.raw_tx);
@@ -312,9 +328,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int mt = tile % p.m_tiles;
-        for (int c = 0; c < p.kc; ++c) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const TcItem it(item, p);
+        const int mt = it.mt;
+        for (int c = it.c0; c < it.c1; ++c) {
           if (!mbar_wait(a_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 2); ok = false; break; }
           mbar_arrive_expect_tx(a_full(s), p.a_tx);
           tma_load_2d(base + L::OFF_A + s * L::A_BYTES, &tmA, a_full(s), c * BK, mt * 128 * MT);
@@ -329,10 +346,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int sa = 0, sb = 0;
       uint32_t pha = 0, phb = 0, phacc = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const TcItem it(item, p);
         if (!mbar_wait(acc_empty, phacc ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 3); ok = false; break; }
         tc_fence_after();
-        for (int c = 0; c < p.kc; ++c) {
+        for (int c = it.c0; c < it.c1; ++c) {
           if (!mbar_wait(a_full(sa), pha, &s_abort) || !mbar_wait(b_full(sb), phb, &s_abort)) {
             atomicExch(&g_tc_status, 4);
             ok = false;
@@ -347,7 +365,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
             for (int h = 0; h < MT; ++h) {
               const uint64_t adesc = kmajor_sw128_desc(a_addr + h * (128 * 128) + kk * 32);
-              tc_mma_f16(tmem_base + h * 256, adesc, bdesc, idesc, (c > 0 || kk > 0) ? 1u : 0u);
+              tc_mma_f16(tmem_base + h * 256, adesc, bdesc, idesc, (c > it.c0 || kk > 0) ? 1u : 0u);
             }
           }
           tc_commit(a_empty(sa));
@@ -367,8 +385,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if constexpr (FMT == kNVFP4) alpha = p.global_scale[0];
     T* C = reinterpret_cast<T*>(p.c);
     const T* bias = reinterpret_cast<const T*>(p.bias);
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+      const TcItem it(item, p);
+      const int mt = it.mt, nt = it.nt;
       if (!mbar_wait(acc_full, ph, &s_abort)) { atomicExch(&g_tc_status, 5); break; }
       ph ^= 1u;
       tc_fence_after();
@@ -381,7 +400,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + h * 256 + cb * 16, v);
           tmem_ld_wait();
           const int col0 = nt * BN + cb * 16;
-          if (row < p.M) {
+          if (p.splits > 1) {
+            // a k slice: raw fp32 sums; scale, bias and rounding happen once, in the reduce kernel
+            if (row < p.M) {
+              uint4* dst = reinterpret_cast<uint4*>(p.partials + ((int64_t)it.slice * p.M + row) * p.N + col0);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            }
+          } else if (row < p.M) {
             uint32_t o[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -408,8 +434,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     int sr = 0, sb = 0;
     uint32_t phr = 0, phb = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      for (int c = 0; c < p.kc; ++c) {
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      const TcItem it(item, p);
+      for (int c = it.c0; c < it.c1; ++c) {
         if (!mbar_wait(raw_full(sr), phr, &s_abort) || !mbar_wait(b_empty(sb), phb ^ 1u, &s_abort)) {
           atomicExch(&g_tc_status, 6);
           ok = false;
@@ -435,6 +462,36 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, NCOLS);
+  }
+}
+
+// Sums the k slices of a split launch in slice order (the same order every run), then applies the
+// nvfp4 global scale and the bias and rounds once.  One thread per eight consecutive columns.
+template <typename T>
+__global__ void __launch_bounds__(256) tc_splitk_reduce_kernel(const TcParams p, bool has_alpha) {
+  const int64_t vecs = (int64_t)p.M * p.N / 8;
+  const int64_t slice_stride = (int64_t)p.M * p.N;
+  const float alpha = has_alpha ? p.global_scale[0] : 1.f;
+  const T* bias = reinterpret_cast<const T*>(p.bias);
+  T* C = reinterpret_cast<T*>(p.c);
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < vecs; v += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t e = v * 8;
+    const int col0 = (int)(e % p.N);
+    const float4* src = reinterpret_cast<const float4*>(p.partials + e);
+    float4 a = src[0], b = src[1];
+    for (int sl = 1; sl < p.splits; ++sl) {
+      const float4* q = reinterpret_cast<const float4*>(p.partials + sl * slice_stride + e);
+      const float4 x = q[0], y = q[1];
+      a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+      b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+    }
+    float r[8] = {a.x * alpha, a.y * alpha, a.z * alpha, a.w * alpha, b.x * alpha, b.y * alpha, b.z * alpha, b.w * alpha};
+    if (bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) r[i] += to_float<T>(bias[bias_index(col0 + i)]);
+    }
+    *reinterpret_cast<uint4*>(C + e) = make_uint4(pack_out<T>(r[0], r[1]), pack_out<T>(r[2], r[3]),
+                                                  pack_out<T>(r[4], r[5]), pack_out<T>(r[6], r[7]));
   }
 }
 
@@ -803,6 +860,32 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 // ---------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------
+// k slices per tile of the dense kernel.  A CTA turns one chunk of packed weights into an operand tile
+// in about 0.75 us (0.93 us with 256-row tiles) whatever else the GPU does, so a launch with fewer tiles
+// than SMs, or a few more, is as slow as its longest CTA.  The estimate below (microseconds) weighs the
+// rounds of work items per CTA against the fp32 partials written and read back and the second launch;
+// slices are used when that wins by a tenth.  A slice keeps at least four chunks.
+int tc_wanted_splits(int64_t M, int64_t N, int64_t K) {
+  if (M <= 16 || N % BN != 0) return 1;
+  const int mt_rows = (M <= 128) ? 128 : 256;
+  const int64_t tiles = ((M + mt_rows - 1) / mt_rows) * (N / BN);
+  const int64_t kc = (K + BK - 1) / BK;
+  const int64_t sms = sm_count();
+  if (tiles <= 0 || sms <= 0) return 1;
+  const double whole = (double)kc * (mt_rows == 128 ? 0.75 : 0.93);
+  const double one = (double)((tiles + sms - 1) / sms) * whole;
+  double best = one * 0.9;
+  int best_s = 1;
+  for (int64_t s = 2; s <= 16 && s <= kc / 4; ++s) {
+    const int64_t bytes = s * M * N * (int64_t)sizeof(float);
+    if (bytes > (128ll << 20)) break;
+    const double rounds = (double)((tiles * s + sms - 1) / sms);
+    const double t = rounds * whole / (double)s + 4.0 + 2.0 * (double)bytes / 5.0e6;
+    if (t < best) { best = t; best_s = (int)s; }
+  }
+  return best_s;
+}
+
 template <typename T, int FMT, int MT>
 int launch_tc(const GemmArgs& g) {
   constexpr int BITS = format_bits(FMT);
@@ -865,10 +948,27 @@ int launch_tc(const GemmArgs& g) {
     attr_set[dev] = true;
   }
   const int tiles = p.m_tiles * p.n_tiles;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  // Fewer tiles than half the SMs: every tile's K range is cut into slices so that the whole GPU streams
+  // weights; as many slices as the caller's scratch has room for.
+  p.splits = tc_wanted_splits(M, N, K);
+  if (p.splits > 1) {
+    const int64_t room = (g.scratch != nullptr) ? g.scratch_bytes / (M * N * (int64_t)sizeof(float)) : 0;
+    if (room < p.splits) p.splits = (int)(room < 2 ? 1 : room);
+  }
+  p.partials = reinterpret_cast<float*>(g.scratch);
+  const int items = tiles * p.splits;
+  const int grid = items < sm_count() ? items : sm_count();
   tc_gemm_kernel<T, FMT, MT><<<grid, THREADS, SMEM, g.stream>>>(tmW, tmA, tmS, tmZ, p);
   MB_CUDA(cudaGetLastError());
   count_launches(1);
+  if (p.splits > 1) {
+    const int64_t vecs = M * N / 8;
+    const int64_t want = (vecs + 255) / 256;
+    const int rgrid = (int)(want < 8 * (int64_t)sm_count() ? want : 8 * (int64_t)sm_count());
+    tc_splitk_reduce_kernel<T><<<rgrid, 256, 0, g.stream>>>(p, FMT == kNVFP4);
+    MB_CUDA(cudaGetLastError());
+    count_launches(1);
+  }
   return 0;
 }
 
@@ -1017,6 +1117,13 @@ int launch_moe_dtype(const GemmArgs& g) {
   return 1;
 }
 }  // namespace
+
+// Room for the fp32 partials of the k slices the dense kernel would like to use for this shape.
+int64_t gemm_tc_scratch_bytes(int64_t m, int64_t n, int64_t k) {
+  if (m <= 16 || n <= 0 || k <= 0) return 0;
+  const int s = tc_wanted_splits(m, n, k);
+  return s > 1 ? (int64_t)s * m * n * (int64_t)sizeof(float) : 0;
+}
 
 // Returns 1 when the problem is not one this kernel takes.
 int launch_gemm_tc(const GemmArgs& g) {

@@ -167,6 +167,44 @@ def test_large_matrix_9_to_16_rows(fmt, dtype, m, group):
     check(out, ref.cpu())
 
 
+@pytest.mark.parametrize("m", [17, 64, 200, 300])
+@pytest.mark.parametrize("fmt,dtype", [("u4b8", torch.float16), ("u4", torch.bfloat16), ("u8b128", torch.float16),
+                                       ("fp8", torch.bfloat16), ("nvfp4", torch.float16), ("mxfp4", torch.bfloat16)])
+def test_k_slices_few_column_tiles(fmt, dtype, m):
+    """More than 16 rows on a matrix of four 256-column tiles: the tensor-memory kernel cuts K into slices
+    (fp32 partials, summed in slice order, bias and the nvfp4 global scale applied after the sum)."""
+    k, n = 4096, 1024
+    a, qw = util.make_dense(m, k, n, fmt, dtype, seed=21)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(22)).to(dtype)
+    out = run_gemm(a, qw, bias=bias)
+    check(out, mo.dense_reference(a, qw.deq, bias=bias))
+    again = run_gemm(a, qw, bias=bias)
+    assert torch.equal(out, again), "the slice sum must be bit-identical from run to run"
+
+
+def test_k_slices_need_scratch_room():
+    """The C ABI takes fewer k slices when the scratch buffer is small, down to none: all three give the
+    oracle's result."""
+    from marlin_v100_b200 import _lib
+    lib = _lib.load()
+    m, k, n = 64, 4096, 1024
+    a, qw = util.make_dense(m, k, n, "u4b8", torch.float16, seed=23)
+    ref = mo.dense_reference(a, qw.deq)
+    d = util.to_dev(qw)
+    a_d = a.cuda()
+    full = lib.marlin_b200_gemm_scratch_bytes(m, n, k, 0)  # format 0 = u4b8, activation type 0 = fp16
+    assert full >= 2 * m * n * 4
+    stream = torch.cuda.current_stream().cuda_stream
+    for nbytes in (full, 2 * m * n * 4 + 64, 1024):
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        c = torch.empty(m, n, dtype=torch.float16, device="cuda")
+        rc = lib.marlin_b200_gemm(a_d.data_ptr(), c.data_ptr(), d.packed.data_ptr(), d.scales.data_ptr(), None, None,
+                                  None, 0, 0, m, n, k, k, d.scales.shape[0], scratch.data_ptr(), nbytes, stream)
+        assert rc == 0, lib.marlin_b200_last_error()
+        torch.cuda.synchronize()
+        check(c, ref)
+
+
 @pytest.mark.parametrize("kw,match", [
     (dict(g_idx=True), "does not support act_order g_idx"),
     (dict(perm=True), "does not support act_order perm"),
