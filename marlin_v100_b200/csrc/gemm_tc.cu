@@ -300,6 +300,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
   const int num_items = p.m_tiles * p.n_tiles * p.splits;
   constexpr int ROWS_PER_KT = (BITS == 4) ? 16 : 32;
+  // the reduce kernel of a split launch may be scheduled now; it waits for this grid's completion itself
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0) {
     // ---------------- packed-weight producer ----------------
@@ -466,32 +468,43 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 }
 
 // Sums the k slices of a split launch in slice order (the same order every run), then applies the
-// nvfp4 global scale and the bias and rounds once.  One thread per eight consecutive columns.
+// nvfp4 global scale and the bias and rounds once.  One thread per four consecutive columns; the loads of
+// four slices are issued before their sums so that their latencies overlap.  Launched as a programmatic
+// dependent of the GEMM kernel: it may start early and waits here for the partials.
 template <typename T>
 __global__ void __launch_bounds__(256) tc_splitk_reduce_kernel(const TcParams p, bool has_alpha) {
-  const int64_t vecs = (int64_t)p.M * p.N / 8;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int64_t vecs = (int64_t)p.M * p.N / 4;
   const int64_t slice_stride = (int64_t)p.M * p.N;
   const float alpha = has_alpha ? p.global_scale[0] : 1.f;
   const T* bias = reinterpret_cast<const T*>(p.bias);
   T* C = reinterpret_cast<T*>(p.c);
   for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < vecs; v += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t e = v * 8;
+    const int64_t e = v * 4;
     const int col0 = (int)(e % p.N);
-    const float4* src = reinterpret_cast<const float4*>(p.partials + e);
-    float4 a = src[0], b = src[1];
-    for (int sl = 1; sl < p.splits; ++sl) {
-      const float4* q = reinterpret_cast<const float4*>(p.partials + sl * slice_stride + e);
-      const float4 x = q[0], y = q[1];
-      a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
-      b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+    const float* src = p.partials + e;
+    float4 a = *reinterpret_cast<const float4*>(src);
+    int sl = 1;
+    for (; sl + 3 < p.splits; sl += 4) {
+      const float4 x0 = *reinterpret_cast<const float4*>(src + sl * slice_stride);
+      const float4 x1 = *reinterpret_cast<const float4*>(src + (sl + 1) * slice_stride);
+      const float4 x2 = *reinterpret_cast<const float4*>(src + (sl + 2) * slice_stride);
+      const float4 x3 = *reinterpret_cast<const float4*>(src + (sl + 3) * slice_stride);
+      a.x = (((a.x + x0.x) + x1.x) + x2.x) + x3.x;
+      a.y = (((a.y + x0.y) + x1.y) + x2.y) + x3.y;
+      a.z = (((a.z + x0.z) + x1.z) + x2.z) + x3.z;
+      a.w = (((a.w + x0.w) + x1.w) + x2.w) + x3.w;
     }
-    float r[8] = {a.x * alpha, a.y * alpha, a.z * alpha, a.w * alpha, b.x * alpha, b.y * alpha, b.z * alpha, b.w * alpha};
+    for (; sl < p.splits; ++sl) {
+      const float4 x = *reinterpret_cast<const float4*>(src + sl * slice_stride);
+      a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+    }
+    float r[4] = {a.x * alpha, a.y * alpha, a.z * alpha, a.w * alpha};
     if (bias != nullptr) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) r[i] += to_float<T>(bias[bias_index(col0 + i)]);
+      for (int i = 0; i < 4; ++i) r[i] += to_float<T>(bias[bias_index(col0 + i)]);
     }
-    *reinterpret_cast<uint4*>(C + e) = make_uint4(pack_out<T>(r[0], r[1]), pack_out<T>(r[2], r[3]),
-                                                  pack_out<T>(r[4], r[5]), pack_out<T>(r[6], r[7]));
+    *reinterpret_cast<uint2*>(C + e) = make_uint2(pack_out<T>(r[0], r[1]), pack_out<T>(r[2], r[3]));
   }
 }
 
@@ -962,11 +975,18 @@ int launch_tc(const GemmArgs& g) {
   MB_CUDA(cudaGetLastError());
   count_launches(1);
   if (p.splits > 1) {
-    const int64_t vecs = M * N / 8;
+    const int64_t vecs = M * N / 4;
     const int64_t want = (vecs + 255) / 256;
-    const int rgrid = (int)(want < 8 * (int64_t)sm_count() ? want : 8 * (int64_t)sm_count());
-    tc_splitk_reduce_kernel<T><<<rgrid, 256, 0, g.stream>>>(p, FMT == kNVFP4);
-    MB_CUDA(cudaGetLastError());
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(want < 8 * (int64_t)sm_count() ? want : 8 * (int64_t)sm_count()));
+    cfg.blockDim = dim3(256);
+    cfg.stream = g.stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MB_CUDA(cudaLaunchKernelEx(&cfg, tc_splitk_reduce_kernel<T>, p, FMT == kNVFP4));
     count_launches(1);
   }
   return 0;
