@@ -320,11 +320,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       for (int i = lane + 8; i < total; i += 4) {
         const int s = i & (STAGES - 1);
         const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
-        if (!mbar_wait(empty(s), ph ^ 1u, &s_abort) || !mbar_wait(mma_done(s), ph ^ 1u, &s_abort)) {
-          atomicExch(&g_dtc_status, 1);
-          break;
-        }
-        issue(i, g, c, true, true);
+        // weights and scales as soon as every shared-memory reader of the stage is done; the digit tile
+        // (the MMA's B operand) only once the MMAs that read the old one have completed
+        if (!mbar_wait(empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_dtc_status, 1); break; }
+        issue(i, g, c, true, false);
+        if (!mbar_wait(mma_done(s), ph ^ 1u, &s_abort)) { atomicExch(&g_dtc_status, 1); break; }
+        issue(i, g, c, false, true);
         c += 4;
         while (c >= p.kc) { c -= p.kc; ++g; }
       }
