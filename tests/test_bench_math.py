@@ -34,5 +34,11 @@ def test_workload_tables_and_selector_names():
     assert b.dominant_kernel("dense_u4_g128_bf16_m16", 16, 8192, 28672) == "decode_tc_kernel"
     assert b.dominant_kernel("dense_u4_g128_bf16_m1", 1, 8192, 28672) == "decode_kernel"
     assert b.dominant_kernel("dense_u4_g128_bf16_m4096", 4096, 8192, 28672) == "tc_gemm_kernel"
+    assert b.dominant_kernel("dense_u4_g128_bf16_m64", 64, 8192, 28672) == "tc_gemm_kernel"
+    # the metric's name follows the row count: weight streaming up to 64 rows, tensor throughput above
+    assert b.metric_name("dense_u4_g128_bf16_m16") == b.METRIC
+    assert b.metric_name("dense_u4_g128_bf16_m64") == b.METRIC_MID
+    assert b.metric_name("dense_u4b8_g128_fp16_m64_k4096") == b.METRIC_MID
+    assert b.metric_name("dense_u4_g128_bf16_m4096") == b.METRIC_COMPUTE
     for name, cfg in b.MOE_WORKLOADS.items():
         assert cfg[2] % 8 == 0 and cfg[7] >= 1, name
