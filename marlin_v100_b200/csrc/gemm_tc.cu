@@ -22,6 +22,7 @@
 // Compiling with -DMB_TC_PROFILE adds per-role wait-cycle counters for CTA 0 and a debug entry point
 // that reads them; release builds carry neither.
 
+#include <cstdint>
 #include "codes.cuh"
 #include "common.cuh"
 #include "tma.cuh"
@@ -70,21 +71,67 @@ struct TcParams {
   int m_tiles, n_tiles;
   uint32_t raw_tx, a_tx;
   int splits;        // k slices per tile; > 1: fp32 partials [slice][M][N], summed by tc_splitk_reduce_kernel
+  int sk;            // > 0: stream-K over (tile, chunk) units with this many CTAs; fp32 partials
+                     // [CTA][2][tile rows][256], summed by tc_streamk_reduce_kernel
   float* partials;
 };
 
 __device__ int g_tc_status = 0;
 
-// A work item of the dense kernel: (tile, k slice), the slice's chunks [c0, c1).
+// A work item of the dense kernel: the chunks [c0, c1) of one tile.  Whole tiles write C; k slices and
+// stream-K segments write fp32 partial sums at partials[pbase + row * pstride + pcol + column].
 struct TcItem {
-  int mt, nt, slice, c0, c1;
-  __device__ TcItem(int item, const TcParams& p) {
+  int mt, nt, c0, c1;
+  bool partial;
+  int64_t pbase;
+  int pstride, pcol;
+};
+
+// The work items of a CTA.  Tile / k-slice mode: items blockIdx.x, blockIdx.x + gridDim.x, ...  Stream-K
+// mode: the (tile, chunk) units are cut into gridDim.x equal ranges, a CTA's range touches at most two
+// tiles (the launch has fewer tiles than CTAs) and each touched tile is one item (segment 0, then 1).
+struct TcWalk {
+  int item, num_items;
+  int64_t u, u1;
+  int seg;
+  __device__ explicit TcWalk(const TcParams& p) {
+    item = blockIdx.x;
+    num_items = p.m_tiles * p.n_tiles * p.splits;
+    const int64_t U = (int64_t)p.m_tiles * p.n_tiles * p.kc;
+    u = (int64_t)blockIdx.x * U / gridDim.x;
+    u1 = (int64_t)(blockIdx.x + 1) * U / gridDim.x;
+    seg = 0;
+  }
+  __device__ bool next(const TcParams& p, int slot_elems, TcItem& it) {
+    if (p.sk > 0) {
+      if (u >= u1) return false;
+      const int tile = (int)(u / p.kc);
+      it.mt = tile % p.m_tiles;
+      it.nt = tile / p.m_tiles;
+      it.c0 = (int)(u - (int64_t)tile * p.kc);
+      const int64_t left = u1 - u;
+      it.c1 = (int)((int64_t)it.c0 + left < (int64_t)p.kc ? (int64_t)it.c0 + left : (int64_t)p.kc);
+      it.partial = !(it.c0 == 0 && it.c1 == p.kc);
+      it.pbase = ((int64_t)blockIdx.x * 2 + seg) * slot_elems - (int64_t)it.mt * (slot_elems / BN) * BN;
+      it.pstride = BN;
+      it.pcol = 0;
+      u += it.c1 - it.c0;
+      ++seg;
+      return true;
+    }
+    if (item >= num_items) return false;
     const int tile = item / p.splits;
-    slice = item - tile * p.splits;
-    mt = tile % p.m_tiles;
-    nt = tile / p.m_tiles;
-    c0 = (int)((int64_t)p.kc * slice / p.splits);
-    c1 = (int)((int64_t)p.kc * (slice + 1) / p.splits);
+    const int slice = item - tile * p.splits;
+    it.mt = tile % p.m_tiles;
+    it.nt = tile / p.m_tiles;
+    it.c0 = (int)((int64_t)p.kc * slice / p.splits);
+    it.c1 = (int)((int64_t)p.kc * (slice + 1) / p.splits);
+    it.partial = p.splits > 1;
+    it.pbase = (int64_t)slice * p.M * p.N;
+    it.pstride = p.N;
+    it.pcol = it.nt * BN;
+    item += gridDim.x;
+    return true;
   }
 };
 
@@ -298,8 +345,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
-  const int num_items = p.m_tiles * p.n_tiles * p.splits;
   constexpr int ROWS_PER_KT = (BITS == 4) ? 16 : 32;
+  constexpr int SLOT_ELEMS = 128 * MT * BN;  // a stream-K partial: the rows of a tile x 256 columns
   // the reduce kernel of a split launch may be scheduled now; it waits for this grid's completion itself
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -309,8 +356,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-        const TcItem it(item, p);
+      TcWalk wk(p);
+      TcItem it;
+      while (ok && wk.next(p, SLOT_ELEMS, it)) {
         const int nt = it.nt;
         for (int c = it.c0; c < it.c1; ++c) {
           if (!mbar_wait(raw_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 1); ok = false; break; }
@@ -330,8 +378,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-        const TcItem it(item, p);
+      TcWalk wk(p);
+      TcItem it;
+      while (ok && wk.next(p, SLOT_ELEMS, it)) {
         const int mt = it.mt;
         for (int c = it.c0; c < it.c1; ++c) {
           if (!mbar_wait(a_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 2); ok = false; break; }
@@ -348,8 +397,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int sa = 0, sb = 0;
       uint32_t pha = 0, phb = 0, phacc = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-        const TcItem it(item, p);
+      TcWalk wk(p);
+      TcItem it;
+      while (ok && wk.next(p, SLOT_ELEMS, it)) {
         if (!mbar_wait(acc_empty, phacc ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 3); ok = false; break; }
         tc_fence_after();
         for (int c = it.c0; c < it.c1; ++c) {
@@ -387,8 +437,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if constexpr (FMT == kNVFP4) alpha = p.global_scale[0];
     T* C = reinterpret_cast<T*>(p.c);
     const T* bias = reinterpret_cast<const T*>(p.bias);
-    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
-      const TcItem it(item, p);
+    TcWalk wk(p);
+    TcItem it;
+    while (wk.next(p, SLOT_ELEMS, it)) {
       const int mt = it.mt, nt = it.nt;
       if (!mbar_wait(acc_full, ph, &s_abort)) { atomicExch(&g_tc_status, 5); break; }
       ph ^= 1u;
@@ -402,10 +453,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + h * 256 + cb * 16, v);
           tmem_ld_wait();
           const int col0 = nt * BN + cb * 16;
-          if (p.splits > 1) {
-            // a k slice: raw fp32 sums; scale, bias and rounding happen once, in the reduce kernel
+          if (it.partial) {
+            // part of a tile's K range: raw fp32 sums; scale, bias and rounding happen once, in the reduce kernel
             if (row < p.M) {
-              uint4* dst = reinterpret_cast<uint4*>(p.partials + ((int64_t)it.slice * p.M + row) * p.N + col0);
+              uint4* dst = reinterpret_cast<uint4*>(p.partials + it.pbase + (int64_t)row * it.pstride + it.pcol + cb * 16);
 #pragma unroll
               for (int i = 0; i < 4; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
             }
@@ -436,8 +487,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     int sr = 0, sb = 0;
     uint32_t phr = 0, phb = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-      const TcItem it(item, p);
+    TcWalk wk(p);
+    TcItem it;
+    while (ok && wk.next(p, SLOT_ELEMS, it)) {
       for (int c = it.c0; c < it.c1; ++c) {
         if (!mbar_wait(raw_full(sr), phr, &s_abort) || !mbar_wait(b_empty(sb), phb ^ 1u, &s_abort)) {
           atomicExch(&g_tc_status, 6);
@@ -503,6 +555,53 @@ __global__ void __launch_bounds__(256) tc_splitk_reduce_kernel(const TcParams p,
     if (bias != nullptr) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) r[i] += to_float<T>(bias[bias_index(col0 + i)]);
+    }
+    *reinterpret_cast<uint2*>(C + e) = make_uint2(pack_out<T>(r[0], r[1]), pack_out<T>(r[2], r[3]));
+  }
+}
+
+// Stream-K: adds, for every tile that more than one CTA worked on, the owners' partial tiles in CTA order,
+// then scale, bias and rounding as above.  CTA q owns the units [q U / P, (q + 1) U / P); the first owner
+// of a tile wrote its second slot unless its range starts with the tile, every later owner its first.
+template <typename T>
+__global__ void __launch_bounds__(256) tc_streamk_reduce_kernel(const TcParams p, int tile_rows, bool has_alpha) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int64_t vecs = (int64_t)p.M * p.N / 4;
+  const int64_t P = p.sk, U = (int64_t)p.m_tiles * p.n_tiles * p.kc;
+  const int64_t slot_elems = (int64_t)tile_rows * BN;
+  const float alpha = has_alpha ? p.global_scale[0] : 1.f;
+  const T* bias = reinterpret_cast<const T*>(p.bias);
+  T* C = reinterpret_cast<T*>(p.c);
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < vecs; v += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t e = v * 4;
+    const int row = (int)(e / p.N), col = (int)(e % p.N);
+    const int nt = col / BN, mt = row / tile_rows;
+    const int64_t tile = (int64_t)nt * p.m_tiles + mt;
+    const int64_t ua = tile * p.kc, ub = ua + p.kc - 1;
+    const int64_t pa = ((ua + 1) * P - 1) / U, pb = ((ub + 1) * P - 1) / U;
+    if (pa == pb) continue;  // one owner: it wrote C itself
+    const int first_slot = (pa * U / P == ua) ? 0 : 1;
+    const float* src = p.partials + (int64_t)(row - mt * tile_rows) * BN + (col - nt * BN);
+    float4 a = *reinterpret_cast<const float4*>(src + (pa * 2 + first_slot) * slot_elems);
+    int64_t q = pa + 1;
+    for (; q + 3 <= pb; q += 4) {
+      const float4 x0 = *reinterpret_cast<const float4*>(src + (q * 2) * slot_elems);
+      const float4 x1 = *reinterpret_cast<const float4*>(src + ((q + 1) * 2) * slot_elems);
+      const float4 x2 = *reinterpret_cast<const float4*>(src + ((q + 2) * 2) * slot_elems);
+      const float4 x3 = *reinterpret_cast<const float4*>(src + ((q + 3) * 2) * slot_elems);
+      a.x = (((a.x + x0.x) + x1.x) + x2.x) + x3.x;
+      a.y = (((a.y + x0.y) + x1.y) + x2.y) + x3.y;
+      a.z = (((a.z + x0.z) + x1.z) + x2.z) + x3.z;
+      a.w = (((a.w + x0.w) + x1.w) + x2.w) + x3.w;
+    }
+    for (; q <= pb; ++q) {
+      const float4 x = *reinterpret_cast<const float4*>(src + (q * 2) * slot_elems);
+      a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+    }
+    float r[4] = {a.x * alpha, a.y * alpha, a.z * alpha, a.w * alpha};
+    if (bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) r[i] += to_float<T>(bias[bias_index(col + i)]);
     }
     *reinterpret_cast<uint2*>(C + e) = make_uint2(pack_out<T>(r[0], r[1]), pack_out<T>(r[2], r[3]));
   }
@@ -873,30 +972,47 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 // ---------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------
-// k slices per tile of the dense kernel.  A CTA turns one chunk of packed weights into an operand tile
-// in about 0.75 us (0.93 us with 256-row tiles) whatever else the GPU does, so a launch with fewer tiles
-// than SMs, or a few more, is as slow as its longest CTA.  The estimate below (microseconds) weighs the
-// rounds of work items per CTA against the fp32 partials written and read back and the second launch;
-// slices are used when that wins by a tenth.  A slice keeps at least four chunks.
-int tc_wanted_splits(int64_t M, int64_t N, int64_t K) {
-  if (M <= 16 || N % BN != 0) return 1;
+// How the dense kernel cuts its work.  A CTA turns one chunk of packed weights into an operand tile in
+// about 0.75 us (0.93 us with 256-row tiles) whatever else the GPU does, so a launch with fewer tiles than
+// SMs, or a few more, is as slow as its longest CTA.  Three ways: whole tiles; k slices (every tile cut
+// into the same number of slices, fp32 partials [slice][M][N]); stream-K (fewer tiles than SMs: the (tile,
+// chunk) units cut into one equal range per SM, fp32 partial tiles per CTA).  The estimates below
+// (microseconds) weigh the chunks of the longest CTA against the partials written and read back and the
+// second launch; a split is used when it wins by a tenth.  A slice keeps at least four chunks.
+struct TcPlan {
+  int splits = 1;
+  int sk = 0;
+  int64_t scratch = 0;
+};
+
+TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int64_t scratch_avail) {
+  TcPlan plan;
+  if (M <= 16 || N % BN != 0) return plan;
   const int mt_rows = (M <= 128) ? 128 : 256;
   const int64_t tiles = ((M + mt_rows - 1) / mt_rows) * (N / BN);
   const int64_t kc = (K + BK - 1) / BK;
   const int64_t sms = sm_count();
-  if (tiles <= 0 || sms <= 0) return 1;
-  const double whole = (double)kc * (mt_rows == 128 ? 0.75 : 0.93);
-  const double one = (double)((tiles + sms - 1) / sms) * whole;
-  double best = one * 0.9;
-  int best_s = 1;
+  if (tiles <= 0 || sms <= 0) return plan;
+  const double chunk_us = (mt_rows == 128 ? 0.75 : 0.93);
+  const double whole = (double)kc * chunk_us;
+  double best = (double)((tiles + sms - 1) / sms) * whole * 0.9;
   for (int64_t s = 2; s <= 16 && s <= kc / 4; ++s) {
     const int64_t bytes = s * M * N * (int64_t)sizeof(float);
-    if (bytes > (128ll << 20)) break;
+    if (bytes > (128ll << 20) || bytes > scratch_avail) break;
     const double rounds = (double)((tiles * s + sms - 1) / sms);
     const double t = rounds * whole / (double)s + 4.0 + 2.0 * (double)bytes / 5.0e6;
-    if (t < best) { best = t; best_s = (int)s; }
+    if (t < best) { best = t; plan.splits = (int)s; plan.sk = 0; plan.scratch = bytes; }
   }
-  return best_s;
+  if (tiles < sms && tiles * kc >= 4 * sms) {
+    const int64_t ctas = sms;
+    const int64_t bytes = ctas * 2 * mt_rows * BN * (int64_t)sizeof(float);
+    // partial tiles actually written: about one per CTA plus one per tile, the valid rows of each
+    const int64_t rows = M < mt_rows ? M : mt_rows;
+    const double moved = (double)(ctas + tiles) * (double)rows * BN * sizeof(float);
+    const double t = (double)((tiles * kc + ctas - 1) / ctas) * chunk_us + 4.0 + 2.0 * moved / 5.0e6;
+    if (bytes <= scratch_avail && t < best) { best = t; plan.splits = 1; plan.sk = (int)ctas; plan.scratch = bytes; }
+  }
+  return plan;
 }
 
 template <typename T, int FMT, int MT>
@@ -961,20 +1077,17 @@ int launch_tc(const GemmArgs& g) {
     attr_set[dev] = true;
   }
   const int tiles = p.m_tiles * p.n_tiles;
-  // Fewer tiles than half the SMs: every tile's K range is cut into slices so that the whole GPU streams
-  // weights; as many slices as the caller's scratch has room for.
-  p.splits = tc_wanted_splits(M, N, K);
-  if (p.splits > 1) {
-    const int64_t room = (g.scratch != nullptr) ? g.scratch_bytes / (M * N * (int64_t)sizeof(float)) : 0;
-    if (room < p.splits) p.splits = (int)(room < 2 ? 1 : room);
-  }
+  // Tiles that would leave SMs idle are cut along K, as far as the caller's scratch has room (tc_plan).
+  const TcPlan plan = tc_plan(M, N, K, g.scratch != nullptr ? g.scratch_bytes : 0);
+  p.splits = plan.splits;
+  p.sk = plan.sk;
   p.partials = reinterpret_cast<float*>(g.scratch);
-  const int items = tiles * p.splits;
-  const int grid = items < sm_count() ? items : sm_count();
+  const int64_t items = p.sk > 0 ? p.sk : (int64_t)tiles * p.splits;
+  const int grid = (int)(items < sm_count() ? items : sm_count());
   tc_gemm_kernel<T, FMT, MT><<<grid, THREADS, SMEM, g.stream>>>(tmW, tmA, tmS, tmZ, p);
   MB_CUDA(cudaGetLastError());
   count_launches(1);
-  if (p.splits > 1) {
+  if (p.splits > 1 || p.sk > 0) {
     const int64_t vecs = M * N / 4;
     const int64_t want = (vecs + 255) / 256;
     cudaLaunchAttribute attr[1];
@@ -986,7 +1099,8 @@ int launch_tc(const GemmArgs& g) {
     cfg.stream = g.stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    MB_CUDA(cudaLaunchKernelEx(&cfg, tc_splitk_reduce_kernel<T>, p, FMT == kNVFP4));
+    if (p.sk > 0) MB_CUDA(cudaLaunchKernelEx(&cfg, tc_streamk_reduce_kernel<T>, p, 128 * MT, FMT == kNVFP4));
+    else MB_CUDA(cudaLaunchKernelEx(&cfg, tc_splitk_reduce_kernel<T>, p, FMT == kNVFP4));
     count_launches(1);
   }
   return 0;
@@ -1141,8 +1255,7 @@ int launch_moe_dtype(const GemmArgs& g) {
 // Room for the fp32 partials of the k slices the dense kernel would like to use for this shape.
 int64_t gemm_tc_scratch_bytes(int64_t m, int64_t n, int64_t k) {
   if (m <= 16 || n <= 0 || k <= 0) return 0;
-  const int s = tc_wanted_splits(m, n, k);
-  return s > 1 ? (int64_t)s * m * n * (int64_t)sizeof(float) : 0;
+  return tc_plan(m, n, k, INT64_MAX).scratch;
 }
 
 // Returns 1 when the problem is not one this kernel takes.

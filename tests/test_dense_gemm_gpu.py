@@ -182,6 +182,32 @@ def test_k_slices_few_column_tiles(fmt, dtype, m):
     assert torch.equal(out, again), "the slice sum must be bit-identical from run to run"
 
 
+@pytest.mark.parametrize("m,dtype", [(32, torch.float16), (130, torch.bfloat16)])
+def test_stream_k_many_column_tiles(m, dtype):
+    """86 column tiles on a 148-SM GPU: the (tile, chunk) units are cut into one equal range per SM, tiles
+    shared by two CTAs are summed from fp32 partial tiles in CTA order (128-row tiles at 32 rows, 256-row
+    tiles at 130).  Parity against (q - 8) * scale in fp32 with bias, all columns, and bit-equality of two runs."""
+    k, n, group = 4096, 22016, 128
+    g = torch.Generator().manual_seed(31)
+    q = torch.randint(0, 16, (k, n), generator=g, dtype=torch.int32)
+    packed = mo.marlin_pack(q, 4).cuda()
+    scales = (torch.rand(k // group, n, generator=g) * 0.01 + 0.001).to(dtype)
+    a = torch.randn(m, k, generator=g).to(dtype)
+    bias = torch.randn(n, generator=g).to(dtype)
+    ops = _ops()
+    ws = torch.empty(0, dtype=torch.int32, device="cuda")
+
+    def run():
+        return ops.marlin_gemm(a.cuda(), None, packed, mo.permute_bias(bias).cuda(), scales.cuda(), None, None, None,
+                               None, None, ws, mo.TYPE_U4B8, m, n, k)
+
+    out = run()
+    w = (q.cuda().float() - 8.0) * scales.cuda().float().repeat_interleave(group, dim=0)
+    ref = a.cuda().float() @ w + bias.cuda().float()
+    check(out, ref.cpu())
+    assert torch.equal(out, run())
+
+
 def test_k_slices_need_scratch_room():
     """The C ABI takes fewer k slices when the scratch buffer is small, down to none: all three give the
     oracle's result."""
