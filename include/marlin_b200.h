@@ -98,10 +98,11 @@ int marlin_b200_awq_repack(const int32_t* b_q_weight, int32_t* out, int64_t size
  * scratch     : device buffer of at least marlin_b200_gemm_scratch_bytes() bytes (may be NULL when
  *               that is 0): fp32 split-K partial sums and, for the integer-MMA kernel, the 8-bit
  *               digit planes of the activation rows.  Contents on entry are irrelevant; it is
- *               overwritten.  For size_m > 16 on matrices with few 256-column tiles the partials are
- *               [k slices][size_m][size_n] fp32; a smaller buffer is accepted there and lowers the
- *               number of k slices (results stay within rounding of each other, and are bit-identical
- *               from run to run for one buffer size).
+ *               overwritten.  For size_m > 16 on matrices whose 256-column tiles would leave SMs idle
+ *               the K range of the tiles is cut and the buffer holds fp32 partial sums ([k slices]
+ *               [size_m][size_n], or two partial tiles per SM); a smaller buffer is accepted there and
+ *               selects a cheaper cut or none (results stay within rounding of each other, and are
+ *               bit-identical from run to run for one buffer size).
  * Requires size_k % 32 == 0 and size_n % 64 == 0.  size_m == 0 is a no-op.
  * -------------------------------------------------------------------------------------------- */
 int64_t marlin_b200_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k, int format);
