@@ -116,9 +116,11 @@ int marlin_b200_gemm(const void* a, void* c, const int32_t* b_q_weight, const vo
 /* Same computation as marlin_b200_gemm, for callers that cannot hand over a scratch buffer because
  * they are not allowed to allocate device memory where the call happens (a serving runtime whose memory
  * plan is fixed at start-up, a plugin that is given tensors but no allocator, host code that runs while
- * another component captures the stream).  The split-K partial sums go to a 6 MiB array inside the
- * library image instead (present on every GPU that loads the library, until the process exits), which
- * covers devices of up to 192 SMs; a larger device gets MARLIN_B200_ESCRATCH and a message.  The call
+ * another component captures the stream).  The scratch is a 6 MiB array inside the library image instead
+ * (present on every GPU that loads the library, until the process exits).  For size_m <= 16 the kernels
+ * need SMs * 32 KiB + 48 * size_k + 256 bytes of it (a 148-SM B200: size_k up to 30 016); a problem beyond
+ * that gets MARLIN_B200_ESCRATCH and a message.  For size_m > 16 the K cut is planned inside the 6 MiB, as
+ * marlin_b200_gemm does with a buffer of that size (results equal that call's bit for bit).  The call
  * allocates nothing.  Its first use on a device resolves the array's device address: do that first
  * call outside any stream capture.  All calls on a device share the array; nothing in it has to start
  * at zero (every partial is written before it is read within one call), but two calls whose kernels

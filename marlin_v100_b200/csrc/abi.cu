@@ -168,6 +168,7 @@ extern "C" int marlin_b200_gemm(const void* a, void* c, const int32_t* b_q_weigh
   g.num_groups = num_groups; g.num_experts = 1; g.top_k = 1;
   g.scratch = scratch; g.scratch_bytes = scratch_bytes; g.stream = (cudaStream_t)stream;
   if (int rc = check_common(g)) return rc;
+  MB_CHECK(scratch == nullptr || ((uintptr_t)scratch & 255) == 0, "scratch must be aligned to 256 bytes");
   MB_CHECK(a_stride % 8 == 0, "A.stride(0) must divisible by 8");
   MB_CHECK(a_stride >= size_k, "A.stride(0) = %lld is smaller than size_k = %lld", (long long)a_stride,
            (long long)size_k);
@@ -205,6 +206,7 @@ extern "C" int marlin_b200_moe_gemm(const void* a, void* c, const int32_t* b_q_w
   MB_CHECK(top_k >= 1, "top_k must be positive, got %d", top_k);
   MB_CHECK(num_experts >= 1, "b_q_weight has no experts");
   if (int rc = check_common(g)) return rc;
+  MB_CHECK(scratch == nullptr || ((uintptr_t)scratch & 255) == 0, "scratch must be aligned to 256 bytes");
   MB_CHECK(sorted_token_ids != nullptr && expert_ids != nullptr && num_tokens_past_padded != nullptr,
            "null routing tensor pointer");
   MB_CHECK(!mul_topk_weights || topk_weights != nullptr, "mul_topk_weights needs topk_weights");

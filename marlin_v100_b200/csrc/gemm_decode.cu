@@ -855,8 +855,11 @@ int read_decode_status(int* value, bool reset) {
 // Dense GEMM with built-in scratch
 // ---------------------------------------------------------------------------------------------------
 namespace {
-// Room for the split-K partial sums of up to 192 SMs (two slots of 16 x 256 floats per SM).
-constexpr int64_t kStaticScratchBytes = 192ll * 2 * 16 * 256 * sizeof(float);  // 6 MiB
+// 6 MiB.  What the M <= 16 kernels need is SMs * 32 KiB of split-K partial sums (two slots of 16 x 256
+// floats per persistent CTA) plus 48 * size_k + 256 bytes for the digit planes of the integer-MMA kernel:
+// on a 148-SM device that fits for size_k up to 30 016.  For M > 16 the tensor-memory kernel plans its
+// k cut inside whatever room it is given, so 6 MiB only limits how finely K is cut.
+constexpr int64_t kStaticScratchBytes = 6ll << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 std::mutex g_static_mutex;
 void* g_static_ptr[64] = {};
@@ -891,13 +894,15 @@ extern "C" int marlin_b200_gemm_static_scratch(const void* a, void* c, const int
     }
     scratch = g_static_ptr[dev];
   }
-  const int64_t need = marlin_b200_gemm_scratch_bytes(size_m, size_n, size_k, format);
-  if (need > kStaticScratchBytes) {
-    set_error("this problem needs %lld bytes of scratch (%d SMs), the built-in scratch holds %lld: use "
-              "marlin_b200_gemm with a caller-provided buffer", (long long)need, sm_count(),
-              (long long)kStaticScratchBytes);
-    return MARLIN_B200_ESCRATCH;
+  // The same routing as marlin_b200_gemm with a 6 MiB buffer: the M > 16 kernel fits its k cut into the
+  // room, the M <= 16 kernels have a fixed need and refuse when it is larger.
+  const int rc = marlin_b200_gemm(a, c, b_q_weight, b_scales, b_zeros, b_bias, global_scale, act_dtype, format,
+                                  size_m, size_n, size_k, a_stride, num_groups, scratch, kStaticScratchBytes, stream);
+  if (rc == MARLIN_B200_ESCRATCH) {
+    set_error("the built-in scratch holds %lld bytes; this problem needs %lld (SMs * 32768 + 48 * size_k + 256 "
+              "with %d SMs, size_k = %lld): use marlin_b200_gemm with a caller-provided buffer",
+              (long long)kStaticScratchBytes, (long long)gemm_decode_scratch_bytes(size_m, size_n, size_k, format),
+              sm_count(), (long long)size_k);
   }
-  return marlin_b200_gemm(a, c, b_q_weight, b_scales, b_zeros, b_bias, global_scale, act_dtype, format, size_m,
-                          size_n, size_k, a_stride, num_groups, scratch, kStaticScratchBytes, stream);
+  return rc;
 }

@@ -371,6 +371,7 @@ extern "C" int marlin_b200_moe_align_block_size(
   MB_CHECK(num_experts > 0 && num_experts <= MAX_SMEM_EXPERTS, "num_experts = %lld out of range (1..%d)",
            (long long)num_experts, MAX_SMEM_EXPERTS);
   MB_CHECK(numel < (1ll << 31), "numel too large");
+  MB_CHECK(scratch == nullptr || ((uintptr_t)scratch & 255) == 0, "scratch must be aligned to 256 bytes");
   const int64_t need = numel + num_experts * (block_size - 1);
   MB_CHECK(sorted_capacity >= (numel == 0 ? 0 : need) || sorted_capacity >= need,
            "sorted_token_ids has %lld entries, needs %lld", (long long)sorted_capacity, (long long)need);

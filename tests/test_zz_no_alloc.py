@@ -57,6 +57,58 @@ def test_static_scratch_matches_regular_entry_point(fmt, dtype, m):
         assert mo.within_tolerance(out.cpu(), mo.dense_reference(a, qw.deq))
 
 
+def _random_problem(m, k, n, dtype, seed):
+    """Random codes and scales made on the device: the comparison below is between two entry points
+    of the library, so no oracle (and no CPU quantiser) is needed."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    a = torch.randn(m, k, generator=g, device="cuda").to(dtype)
+    packed = torch.randint(-2**31, 2**31 - 1, (k // 16, n * 2), generator=g, device="cuda", dtype=torch.int32)
+    scales = (torch.rand(k // 128, n, generator=g, device="cuda") * 0.01 + 0.002).to(dtype)
+    return a, packed, scales
+
+
+# (m, k, n): the M > 16 kernel cutting K into slices that fit the built-in 6 MiB; a shape where no cut
+# fits (whole tiles); 12 rows on a matrix of 2^27 weights (the integer-MMA kernel: its digit planes sit
+# behind the partial sums in the scratch)
+@pytest.mark.parametrize("m,k,n", [(64, 4096, 4096), (64, 4096, 22016), (12, 8192, 16384)])
+def test_static_scratch_larger_shapes(m, k, n):
+    from marlin_v100_b200 import _lib
+    lib = _lib.load()
+    dtype = torch.float16
+    a, packed, scales = _random_problem(m, k, n, dtype, seed=m + n)
+    stream = torch.cuda.current_stream().cuda_stream
+    six_mib = 6 << 20
+    scratch = torch.empty(six_mib, dtype=torch.uint8, device="cuda")
+    ref_out = torch.empty(m, n, dtype=dtype, device="cuda")
+    _lib.check(lib.marlin_b200_gemm(a.data_ptr(), ref_out.data_ptr(), packed.data_ptr(), scales.data_ptr(), None,
+                                    None, None, 0, 0, m, n, k, k, k // 128, scratch.data_ptr(), six_mib, stream))
+    for _ in range(2):
+        out = torch.full((m, n), float("nan"), dtype=dtype, device="cuda")
+        before = torch.cuda.memory_allocated()
+        _lib.check(lib.marlin_b200_gemm_static_scratch(a.data_ptr(), out.data_ptr(), packed.data_ptr(),
+                                                       scales.data_ptr(), None, None, None, 0, 0, m, n, k, k,
+                                                       k // 128, stream))
+        assert torch.cuda.memory_allocated() == before
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref_out)
+    assert not torch.isnan(ref_out.float()).any()
+
+
+def test_static_scratch_refuses_what_does_not_fit():
+    """K so large that the M <= 16 kernels' fixed need (SMs * 32 KiB + 48 * K + 256) passes 6 MiB."""
+    from marlin_v100_b200 import _lib
+    lib = _lib.load()
+    m, k, n = 4, 65536, 256
+    a, packed, scales = _random_problem(m, k, n, torch.float16, seed=5)
+    out = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+    rc = lib.marlin_b200_gemm_static_scratch(a.data_ptr(), out.data_ptr(), packed.data_ptr(), scales.data_ptr(),
+                                             None, None, None, 0, 0, m, n, k, k, k // 128,
+                                             torch.cuda.current_stream().cuda_stream)
+    assert rc == -3
+    msg = lib.marlin_b200_last_error()
+    assert b"built-in scratch holds 6291456 bytes" in msg and b"marlin_b200_gemm" in msg
+
+
 def test_static_scratch_argument_error_is_reported():
     from marlin_v100_b200 import _lib
     lib = _lib.load()
