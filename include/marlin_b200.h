@@ -40,6 +40,10 @@ extern "C" {
 #define MARLIN_B200_FMT_NVFP4 5
 #define MARLIN_B200_FMT_MXFP4 6
 
+/* Flag, or-ed into the `format` argument of marlin_b200_gemm / marlin_b200_gemm_scratch_bytes: b_q_weight is
+ * in the library's streaming layout (made by marlin_b200_prepare_weights), not in the reference layout. */
+#define MARLIN_B200_FMT_PREPARED 0x100
+
 /* Scale element kinds for marlin_b200_format_from_type_id(). */
 #define MARLIN_B200_SCALE_ACT 0  /* same 16-bit type as the activations */
 #define MARLIN_B200_SCALE_E4M3 1 /* nvfp4 block scales */
@@ -57,8 +61,8 @@ int64_t marlin_b200_launch_count(void);
 /* Diagnostic (no reference counterpart): every wait inside the pipelined kernels is bounded (about two
  * seconds); a kernel whose wait gave up drains without touching its output and leaves a code here.
  * *status = 0 when no kernel on the current device gave up since the last reset; otherwise byte 0 /
- * 1 / 2 hold the code of the register-fragment decode kernel / the tensor-memory kernels / the
- * integer-MMA decode kernel.  Synchronises with the device: call it outside the hot path. */
+ * 1 / 2 / 3 hold the code of the register-fragment decode kernel / the tensor-memory kernels / the
+ * integer-MMA decode kernel / the weight-streaming kernel.  Synchronises with the device: call it outside the hot path. */
 int marlin_b200_kernel_status(int* status, int reset);
 
 /* Maps (b_type_id, scale kind) to a MARLIN_B200_FMT_* value, or -1.
@@ -79,6 +83,26 @@ int marlin_b200_gptq_repack(const int32_t* b_q_weight, const int32_t* perm, int3
                             int64_t size_k, int64_t size_n, int num_bits, void* stream);
 int marlin_b200_awq_repack(const int32_t* b_q_weight, int32_t* out, int64_t size_k, int64_t size_n,
                            int num_bits, void* stream);
+
+/* ----------------------------------------------------------------------------------------------
+ * Streaming layout (opt-in).  The reference's packed layout stores a 256-column group of 16 k as a run of
+ * 2 KiB (4 KiB for 8-bit codes) and the next 16 k size_n * 8 bytes further on; read as a stream that
+ * pattern reaches about two thirds of the DRAM bandwidth of a linear read, and its nibble order forces byte
+ * transposes in the kernel.  marlin_b200_prepare_weights writes the SAME codes in another order (every
+ * 256-column x 64-k block contiguous, blocks of a column group consecutive along k, codes placed where the
+ * GEMM kernel's threads consume them); marlin_b200_restore_weights is its exact inverse, so
+ * restore(prepare(w)) == w bit for bit and both tensors have size_k * size_n * num_bits / 8 bytes per expert.
+ * This is the "TMA-friendly packed layout that stays bit-identical in unpacked semantics"; what
+ * gptq_marlin_repack / awq_marlin_repack return is unchanged (csrc/quantization/marlin/
+ * gptq_marlin_repack.cu:399-469 defines it), a caller converts once after repacking and then passes
+ * `format | MARLIN_B200_FMT_PREPARED` to marlin_b200_gemm.  The reference has no counterpart of the two
+ * entry points.  b_q_weight / out: int32 [num_experts, size_k / 16, size_n * 16 / pf]; out must not alias
+ * the input.  Requires size_k % 128 == 0 and size_n % 256 == 0 (other shapes stay in the reference layout).
+ * -------------------------------------------------------------------------------------------- */
+int marlin_b200_prepare_weights(const int32_t* b_q_weight, int32_t* out, int64_t size_k, int64_t size_n,
+                                int num_bits, int64_t num_experts, void* stream);
+int marlin_b200_restore_weights(const int32_t* prepared, int32_t* out, int64_t size_k, int64_t size_n,
+                                int num_bits, int64_t num_experts, void* stream);
 
 /* ----------------------------------------------------------------------------------------------
  * Dense GEMM  C[M,N] = A[M,K] * dequant(B)[K,N] (+ bias).  Stands in for
@@ -103,6 +127,11 @@ int marlin_b200_awq_repack(const int32_t* b_q_weight, int32_t* out, int64_t size
  *               [size_m][size_n], or two partial tiles per SM); a smaller buffer is accepted there and
  *               selects a cheaper cut or none (results stay within rounding of each other, and are
  *               bit-identical from run to run for one buffer size).
+ * With MARLIN_B200_FMT_PREPARED in `format`, b_q_weight is the streaming layout and one kernel family serves
+ * every size_m (passes of up to 128 rows); scratch then holds one counter per 256-column group and two fp32
+ * partial tiles per SM, and a buffer that is too small (or NULL) makes every CTA take whole column groups
+ * instead of equal shares of the weight stream (slower when size_n / 256 does not fill the SMs, same results
+ * up to the order of the fp32 sums).
  * Requires size_k % 32 == 0 and size_n % 64 == 0.  size_m == 0 is a no-op.
  * -------------------------------------------------------------------------------------------- */
 int64_t marlin_b200_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k, int format);

@@ -22,6 +22,8 @@ SIGNATURES = {
     "marlin_b200_format_from_type_id": (_int, [_i64, _int]),
     "marlin_b200_gptq_repack": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp]),
     "marlin_b200_awq_repack": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
+    "marlin_b200_prepare_weights": (_int, [_vp, _vp, _i64, _i64, _int, _i64, _vp]),
+    "marlin_b200_restore_weights": (_int, [_vp, _vp, _i64, _i64, _int, _i64, _vp]),
     "marlin_b200_gemm_scratch_bytes": (_i64, [_i64, _i64, _i64, _int]),
     "marlin_b200_gemm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _i64, _i64, _i64, _i64,
                                 _i64, _vp, _i64, _vp]),
@@ -39,6 +41,8 @@ SIGNATURES = {
     "marlin_b200_moe_sum": (_int, [_vp, _vp, _i64, _int, _i64, _int, _vp]),
     "marlin_b200_moe_sum_rows": (_int, [_vp, _vp, _vp, _i64, _int, _i64, _int, _vp]),
 }
+
+FMT_PREPARED = 0x100  # MARLIN_B200_FMT_PREPARED
 
 _lib = None
 

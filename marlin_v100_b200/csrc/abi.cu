@@ -6,6 +6,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "stream_layout.cuh"
 
 namespace mb200 {
 
@@ -99,6 +100,12 @@ int dispatch(const GemmArgs& g) {
     set_error("size_k must be positive");
     return MARLIN_B200_EINVAL;
   }
+  if (g.prepared) {
+    // weights in the streaming layout: one kernel family for every size_m
+    MB_CHECK(stream::layout_accepts(g.size_k, g.size_n),
+             "weights in the streaming layout need size_k %% 128 == 0 and size_n %% 256 == 0");
+    return g.act_dtype == MARLIN_B200_F16 ? launch_gemm_stream_f16(g) : launch_gemm_stream_bf16(g);
+  }
   // M <= 16: weight-streaming kernel.  Larger M: tensor-memory kernel; shapes it does not take fall
   // back to passes of the streaming kernel, and anything else to the shape-agnostic kernel.
   if (g.size_m > 16) {
@@ -128,11 +135,14 @@ extern "C" int64_t marlin_b200_launch_count(void) { return g_launches.load(std::
 
 extern "C" int marlin_b200_kernel_status(int* status, int reset) {
   MB_CHECK(status != nullptr, "null status pointer");
-  int a = 0, b = 0, c = 0;
+  int a = 0, b = 0, c = 0, d = 0, e = 0;
   if (int rc = read_decode_status(&a, reset != 0)) return rc;
   if (int rc = read_tc_status(&b, reset != 0)) return rc;
   if (int rc = read_decode_tc_status(&c, reset != 0)) return rc;
-  *status = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16);
+  if (int rc = read_stream_status_f16(&d, reset != 0)) return rc;
+  if (int rc = read_stream_status_bf16(&e, reset != 0)) return rc;
+  if (d == 0) d = e;
+  *status = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | ((d & 0xff) << 24);
   return 0;
 }
 
@@ -151,6 +161,7 @@ extern "C" int marlin_b200_format_from_type_id(int64_t id, int scale_kind) {
 
 extern "C" int64_t marlin_b200_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k,
                                                   int format) {
+  if (format & MARLIN_B200_FMT_PREPARED) return gemm_stream_scratch_bytes(size_m, size_n, size_k);
   const int64_t a = gemm_decode_scratch_bytes(size_m, size_n, size_k, format);
   const int64_t b = gemm_tc_scratch_bytes(size_m, size_n, size_k);
   return a > b ? a : b;
@@ -163,7 +174,8 @@ extern "C" int marlin_b200_gemm(const void* a, void* c, const int32_t* b_q_weigh
                                 int64_t scratch_bytes, void* stream) {
   GemmArgs g{};
   g.a = a; g.c = c; g.bq = b_q_weight; g.scales = b_scales; g.zeros = b_zeros; g.bias = b_bias;
-  g.global_scale = global_scale; g.act_dtype = act_dtype; g.format = format;
+  g.global_scale = global_scale; g.act_dtype = act_dtype; g.format = format & ~MARLIN_B200_FMT_PREPARED;
+  g.prepared = (format & MARLIN_B200_FMT_PREPARED) != 0;
   g.size_m = size_m; g.size_n = size_n; g.size_k = size_k; g.a_stride = a_stride;
   g.num_groups = num_groups; g.num_experts = 1; g.top_k = 1;
   g.scratch = scratch; g.scratch_bytes = scratch_bytes; g.stream = (cudaStream_t)stream;
@@ -199,6 +211,8 @@ extern "C" int marlin_b200_moe_gemm(const void* a, void* c, const int32_t* b_q_w
   g.topk_weights = topk_weights; g.num_sorted = num_sorted; g.num_experts = num_experts;
   g.block_size = moe_block_size; g.top_k = top_k; g.mul_topk = mul_topk_weights;
   g.scratch = scratch; g.scratch_bytes = scratch_bytes; g.stream = (cudaStream_t)stream;
+  MB_CHECK((format & MARLIN_B200_FMT_PREPARED) == 0,
+           "the grouped GEMM takes expert weights in the reference layout, not the streaming layout");
   if (moe_block_size != 8) {
     MB_CHECK(moe_block_size % 16 == 0 && moe_block_size >= 16 && moe_block_size <= 64,
              "unsupported moe_block_size=%d", moe_block_size);

@@ -14,13 +14,21 @@ namespace codes {
 template <typename T> constexpr bool kHalf = false;
 template <> constexpr bool kHalf<__half> = true;
 
+// a - b as a fused multiply-add, a * 1 + (-b): the same result (one rounding), but issued to the FMA pipe.
+// The packed 16-bit add / subtract was measured to occupy the half-rate ALU pipe that the shifts and logic
+// operations of the decoders already fill.
 template <typename T>
 __device__ __forceinline__ uint32_t psub(uint32_t a, uint32_t b) {
+  const uint32_t nb = b ^ 0x80008000u;
   if constexpr (kHalf<T>) {
-    __half2 r = __hsub2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    const uint32_t one = 0x3C003C00u;
+    __half2 r = __hfma2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<const __half2*>(&one),
+                        *reinterpret_cast<const __half2*>(&nb));
     return *reinterpret_cast<uint32_t*>(&r);
   } else {
-    __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    const uint32_t one = 0x3F803F80u;
+    __nv_bfloat162 r = __hfma2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&one),
+                               *reinterpret_cast<const __nv_bfloat162*>(&nb));
     return *reinterpret_cast<uint32_t*>(&r);
   }
 }

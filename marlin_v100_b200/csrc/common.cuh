@@ -157,6 +157,7 @@ struct GemmArgs {
   void* scratch;
   int64_t scratch_bytes;
   cudaStream_t stream;
+  bool prepared;  // b_q_weight is in the streaming layout (stream_layout.cuh)
 };
 
 // kernel launchers (one per translation unit)
@@ -165,10 +166,15 @@ int launch_gemm_decode(const GemmArgs& g);          // returns 1 if the shape is
 int64_t gemm_decode_scratch_bytes(int64_t m, int64_t n, int64_t k, int format);
 int launch_gemm_decode_tc(const GemmArgs& g);       // returns 1 if the shape is not handled
 int launch_gemm_tc(const GemmArgs& g);              // returns 1 if the shape is not handled
+int launch_gemm_stream_f16(const GemmArgs& g);      // weights in the streaming layout
+int launch_gemm_stream_bf16(const GemmArgs& g);
+int64_t gemm_stream_scratch_bytes(int64_t m, int64_t n, int64_t k);
 int64_t gemm_tc_scratch_bytes(int64_t m, int64_t n, int64_t k);
 // give-up words of the three pipelined kernel families (0 = every wait completed)
 int read_decode_status(int* value, bool reset);
 int read_tc_status(int* value, bool reset);
 int read_decode_tc_status(int* value, bool reset);
+int read_stream_status_f16(int* value, bool reset);
+int read_stream_status_bf16(int* value, bool reset);
 
 }  // namespace mb200

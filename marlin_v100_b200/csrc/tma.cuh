@@ -84,6 +84,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// The same bounded wait for warps that expect to wait long (an epilogue waiting for a whole run of chunks, a
+// producer or MMA issuer that is ahead of the other warps): between polls the warp sleeps `ns` nanoseconds,
+// so it does not take issue slots from the warps that do the arithmetic.
+__device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i) {
+      __nanosleep(ns);
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*abort_flag != 0) return false;
+    if (global_timer_ns() - t0 > 2000000000ull) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
                                             int c1) {
   asm volatile(
@@ -126,6 +145,11 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
 __device__ __forceinline__ uint32_t lds16(uint32_t addr) {

@@ -8,6 +8,8 @@ shapes) live here; everything that only needs pointers and sizes is checked agai
 Every launch goes to the current CUDA stream of the tensor's device; nothing synchronises."""
 from __future__ import annotations
 
+import weakref
+
 import torch
 
 from . import _lib
@@ -137,6 +139,52 @@ def awq_marlin_moe_repack(b_q_weight: torch.Tensor, perm: torch.Tensor | None, s
     for i in range(e):
         out[i] = awq_marlin_repack(b_q_weight[i], size_k, size_n, num_bits, is_a_8bit)
     return out
+
+
+# --------------------------------------------------------------------------------------------
+# streaming layout (opt-in; no counterpart in the reference)
+# --------------------------------------------------------------------------------------------
+
+# data_ptr -> (size_k, size_n, num_bits) of every live tensor made by `prepare_weights`; an entry is
+# dropped when its tensor is freed, so a later allocation at the same address is not mistaken for one.
+_PREPARED: dict[int, tuple[int, int, int]] = {}
+
+
+def _convert_layout(fn_name: str, w: torch.Tensor, size_k: int, size_n: int, num_bits: int) -> torch.Tensor:
+    lib = _lib.load()
+    _check(w.is_cuda and w.is_contiguous() and w.dtype == torch.int32,
+           "packed weights must be a contiguous int32 CUDA tensor")
+    _check(w.dim() in (2, 3), "packed weights must be [K/16, N*16/pf] or [E, K/16, N*16/pf]")
+    pf = 32 // num_bits
+    _check(w.size(-2) == size_k // 16 and w.size(-1) == size_n * 16 // pf,
+           f"Shape mismatch: b_q_weight = {tuple(w.shape)}, size_k = {size_k}, size_n = {size_n}")
+    experts = w.size(0) if w.dim() == 3 else 1
+    with torch.cuda.device(w.device):
+        out = torch.empty_like(w)
+        _lib.check(getattr(lib, fn_name)(_ptr(w), _ptr(out), size_k, size_n, num_bits, experts, _stream(w.device)))
+    return out
+
+
+def prepare_weights(b_q_weight: torch.Tensor, size_k: int, size_n: int, num_bits: int) -> torch.Tensor:
+    """Returns the same codes in the library's streaming layout (every 256-column x 64-k block contiguous,
+    codes where the GEMM threads consume them).  Call once after `gptq_marlin_repack` / `awq_marlin_repack`
+    and pass the result to `marlin_gemm` in place of the repacked tensor: it is recognised by its address.
+    Needs size_k % 128 == 0 and size_n % 256 == 0."""
+    out = _convert_layout("marlin_b200_prepare_weights", b_q_weight, size_k, size_n, num_bits)
+    ptr = out.data_ptr()
+    _PREPARED[ptr] = (size_k, size_n, num_bits)
+    weakref.finalize(out, _PREPARED.pop, ptr, None)
+    return out
+
+
+def restore_weights(prepared: torch.Tensor, size_k: int, size_n: int, num_bits: int) -> torch.Tensor:
+    """Inverse of `prepare_weights`: the reference layout again, bit for bit."""
+    return _convert_layout("marlin_b200_restore_weights", prepared, size_k, size_n, num_bits)
+
+
+def is_prepared(b_q_weight: torch.Tensor, size_k: int, size_n: int) -> bool:
+    entry = _PREPARED.get(b_q_weight.data_ptr())
+    return entry is not None and entry[0] == size_k and entry[1] == size_n
 
 
 # --------------------------------------------------------------------------------------------
@@ -338,10 +386,11 @@ def _gemm_prepare(a, c, b_q_weight, b_bias, b_scales, a_scales, global_scale, b_
             _check(not is_zp_float, "is_zp_float is true but b_zeros was not provided.")
             _check(fmt not in (1, 3), "Marlin uint4/uint8 dense path requires float zero points.")
 
-        nbytes = lib.marlin_b200_gemm_scratch_bytes(size_m, size_n, size_k, fmt)
+        fmt_arg = fmt | (_lib.FMT_PREPARED if is_prepared(b_q_weight, size_k, size_n) else 0)
+        nbytes = lib.marlin_b200_gemm_scratch_bytes(size_m, size_n, size_k, fmt_arg)
         scratch = _scratch(nbytes, a.device)
         args = (_ptr(a), _ptr(c), _ptr(b_q_weight), _ptr(b_scales), _ptr(b_zeros) if has_zp else None,
-                _ptr(b_bias), _ptr(global_scale), act, fmt, size_m, size_n, size_k, a.stride(0), num_groups,
+                _ptr(b_bias), _ptr(global_scale), act, fmt_arg, size_m, size_n, size_k, a.stride(0), num_groups,
                 _ptr(scratch), nbytes)
         device, fn = a.device, lib.marlin_b200_gemm
 

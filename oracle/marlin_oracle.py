@@ -143,6 +143,46 @@ def marlin_unpack(packed: torch.Tensor, size_k: int, size_n: int, bits: int) -> 
     return vals.to(torch.int32).contiguous()
 
 
+def stream_layout_pack(q: torch.Tensor, bits: int) -> torch.Tensor:
+    """[K, N] ints -> int32 [K/16, N*16/pf]: the same codes as :func:`marlin_pack` in the streaming
+    layout of the B200 library (no counterpart in the reference; the statement of the layout is
+    ``marlin_v100_b200/csrc/stream_layout.cuh``).  Word order [column group of 256][k // 64][n % 256 // 16]
+    then, 4-bit: [n % 8][k % 16 // 4][k % 64 // 16], nibble = (k % 2) * 4 + (k % 4 // 2) * 2 + (n % 16 // 8);
+    8-bit: [k % 64 // 32][n % 8][k % 16 // 4][k % 32 // 16][k % 4 // 2], byte = (n % 16 // 8) * 2 + k % 2."""
+    pf = 32 // bits
+    k, n = q.shape
+    if k % 128 or n % 256:
+        raise ValueError(f"need K % 128 == 0 and N % 256 == 0, got {(k, n)}")
+    a = q.to(torch.int64)
+    if bits == 4:
+        # k = kb*64 + j*16 + t*4 + e2*2 + e1 ; n = grp*256 + slab*16 + hi*8 + g8
+        a = a.reshape(k // 64, 4, 4, 2, 2, n // 256, 16, 2, 8)       # kb j t e2 e1 grp slab hi g8
+        a = a.permute(5, 0, 6, 8, 2, 1, 4, 3, 7)                      # grp kb slab g8 t j | e1 e2 hi
+    else:
+        a = a.reshape(k // 64, 2, 2, 4, 2, 2, n // 256, 16, 2, 8)    # kb jh jl t y e1 grp slab hi g8
+        a = a.permute(6, 0, 7, 1, 9, 3, 2, 4, 8, 5)                   # grp kb slab jh g8 t jl y | hi e1
+    a = a.reshape(-1, pf)
+    shifts = (torch.arange(pf, dtype=torch.int64) * bits).reshape(1, pf)
+    word = (a << shifts).sum(dim=-1) & 0xFFFFFFFF
+    return _to_i32(word).reshape(k // 16, n * 16 // pf)
+
+
+def stream_layout_unpack(packed: torch.Tensor, size_k: int, size_n: int, bits: int) -> torch.Tensor:
+    """Inverse of :func:`stream_layout_pack` -> int32 [K, N]."""
+    pf = 32 // bits
+    w = (packed.to(torch.int64) & 0xFFFFFFFF).reshape(-1, 1)
+    shifts = (torch.arange(pf, dtype=torch.int64) * bits).reshape(1, pf)
+    v = (w >> shifts) & ((1 << bits) - 1)
+    k, n = size_k, size_n
+    if bits == 4:
+        v = v.reshape(n // 256, k // 64, 16, 8, 4, 4, 2, 2, 2)       # grp kb slab g8 t j e1 e2 hi
+        v = v.permute(1, 5, 4, 7, 6, 0, 2, 8, 3)                      # kb j t e2 e1 grp slab hi g8
+    else:
+        v = v.reshape(n // 256, k // 64, 16, 2, 8, 4, 2, 2, 2, 2)    # grp kb slab jh g8 t jl y hi e1
+        v = v.permute(1, 3, 6, 5, 7, 9, 0, 2, 8, 4)                   # kb jh jl t y e1 grp slab hi g8
+    return v.reshape(k, n).to(torch.int32).contiguous()
+
+
 def gptq_marlin_repack(b_q_weight: torch.Tensor, perm: torch.Tensor | None, size_k: int,
                        size_n: int, bits: int) -> torch.Tensor:
     """Oracle of the repack op: unpack GPTQ words, gather rows by ``perm`` (act-order), re-pack
