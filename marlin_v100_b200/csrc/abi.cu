@@ -104,6 +104,7 @@ int dispatch(const GemmArgs& g) {
     // weights in the streaming layout: one kernel family for every size_m
     MB_CHECK(stream::layout_accepts(g.size_k, g.size_n),
              "weights in the streaming layout need size_k %% 128 == 0 and size_n %% 256 == 0");
+    if (gemm_stream_i8_accepts(g)) return launch_gemm_stream_i8(g);
     return g.act_dtype == MARLIN_B200_F16 ? launch_gemm_stream_f16(g) : launch_gemm_stream_bf16(g);
   }
   // M <= 16: weight-streaming kernel.  Larger M: tensor-memory kernel; shapes it does not take fall
@@ -142,6 +143,10 @@ extern "C" int marlin_b200_kernel_status(int* status, int reset) {
   if (int rc = read_stream_status_f16(&d, reset != 0)) return rc;
   if (int rc = read_stream_status_bf16(&e, reset != 0)) return rc;
   if (d == 0) d = e;
+  if (d == 0) {
+    if (int rc = read_stream_i8_status(&d, reset != 0)) return rc;
+    if (d != 0) d |= 0x80;
+  }
   *status = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | ((d & 0xff) << 24);
   return 0;
 }
@@ -161,7 +166,12 @@ extern "C" int marlin_b200_format_from_type_id(int64_t id, int scale_kind) {
 
 extern "C" int64_t marlin_b200_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k,
                                                   int format) {
-  if (format & MARLIN_B200_FMT_PREPARED) return gemm_stream_scratch_bytes(size_m, size_n, size_k);
+  if (format & MARLIN_B200_FMT_PREPARED) {
+    const int64_t a = gemm_stream_scratch_bytes(size_m, size_n, size_k);
+    const int f = format & ~MARLIN_B200_FMT_PREPARED;
+    const int64_t b = (size_m <= 16 && (f == kU4B8 || f == kU4)) ? gemm_stream_i8_scratch_bytes(size_m, size_n, size_k) : 0;
+    return a > b ? a : b;
+  }
   const int64_t a = gemm_decode_scratch_bytes(size_m, size_n, size_k, format);
   const int64_t b = gemm_tc_scratch_bytes(size_m, size_n, size_k);
   return a > b ? a : b;

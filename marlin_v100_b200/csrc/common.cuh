@@ -169,6 +169,9 @@ int launch_gemm_tc(const GemmArgs& g);              // returns 1 if the shape is
 int launch_gemm_stream_f16(const GemmArgs& g);      // weights in the streaming layout
 int launch_gemm_stream_bf16(const GemmArgs& g);
 int64_t gemm_stream_scratch_bytes(int64_t m, int64_t n, int64_t k);
+bool gemm_stream_i8_accepts(const GemmArgs& g);     // integer-MMA kernel for M <= 16, 4-bit integer formats
+int launch_gemm_stream_i8(const GemmArgs& g);
+int64_t gemm_stream_i8_scratch_bytes(int64_t m, int64_t n, int64_t k);
 int64_t gemm_tc_scratch_bytes(int64_t m, int64_t n, int64_t k);
 // give-up words of the three pipelined kernel families (0 = every wait completed)
 int read_decode_status(int* value, bool reset);
@@ -176,5 +179,6 @@ int read_tc_status(int* value, bool reset);
 int read_decode_tc_status(int* value, bool reset);
 int read_stream_status_f16(int* value, bool reset);
 int read_stream_status_bf16(int* value, bool reset);
+int read_stream_i8_status(int* value, bool reset);
 
 }  // namespace mb200

@@ -1,0 +1,679 @@
+// Decode-sized GEMM (M <= 16 rows) for 4-bit integer weights in the streaming layout (stream_layout.cuh):
+// integer MMAs on 8-bit operands, weights as the tensor-memory operand.
+//
+//   C[M, N] = A[M, K] * dequant(Wq)[K, N] (+ bias)      (reference operator: csrc/quantization/marlin/marlin.cu:83)
+//
+// Why integers: a tcgen05.mma whose 128-row operand comes from tensor memory costs about 45 cycles of the SM
+// partitions' issue bandwidth whatever its N, so the number of MMAs per weight byte bounds the stream.  With
+// 8-bit operands (kind::i8, K = 32) a 16 KiB chunk takes 8 MMAs and two logic instructions per packed word;
+// with 16-bit operands it takes 16 MMAs and fifteen instructions per word.
+//
+// The contraction runs transposed, D[n, m] = sum_k W[k, n] * A[m, k]: the 128 rows of an MMA are 128 weight
+// columns, its N = 32 are two digit planes of 16 token columns, accumulation is exact (s32).
+//  * Weights.  A word of the streaming layout holds the codes of two columns (8 apart) at four k, one column
+//    in the low nibbles, the other in the high nibbles of its bytes.  `w & 0x0f0f0f0f` is the first column's
+//    byte quadruple (byte = q); `(w ^ 0x80808080) & 0xf0f0f0f0` the second one's (byte = 16 (q - 8) as a signed
+//    byte).  Byte = alpha (q - beta) with (alpha, beta) = (1, 0) or (16, 8), fixed per tensor-memory lane.
+//  * Activations.  act_digits_kernel (in front, chained by programmatic dependent launch) rewrites every row as
+//    two signed 8-bit digits, a = 2^(e-7) (d1 + d2 / 2^8), e from the row maximum (|d1| <= 127): 16 bits of
+//    fixed point under the row maximum, i.e. exact for every bf16 element within 2^-8 of the row maximum (fp16:
+//    2^-5), absolute error <= 2^(e-16) otherwise; the row factor 2^(e-7) is exact.  Digits are stored in the k
+//    order in which the weight bytes land in tensor memory (a fixed permutation inside every 128 k).  The kernel
+//    also leaves, per row and 128-k chunk, the sum of the row's digits (what the zero-point and offset terms
+//    multiply), and it clears the column-group counters of the reduction.
+// Scales are applied after the MMA, per 128-k chunk: with V = 256 D1 + D2 (an exact integer) and SA the chunk's
+// digit sum, acc += (s / (256 alpha)) V + (s (beta - zero) - zs) SA  (zero = 8 for u4b8; zs = zero-point times
+// scale as passed for u4).  The row factor and the bias are applied once per column group.
+//
+// Work split: persistent CTAs, one per SM, each owning a contiguous range of (256-column group, 128-k chunk)
+// units = one linear range of weight bytes.  Column groups shared between CTAs leave fp32 partial sums in
+// scratch; the CTA that arrives last at the group's counter adds them in CTA order (no waiting; bit-identical
+// from run to run).
+//
+// Warps (640 threads, so that nothing spills): 0-7 epilogue (tile = warp / 4, 32-lane quadrant = warp % 4) |
+// 8-15 dequant (quadrant = warp % 4, tile = (warp - 8) / 4; both 16-lane halves) | 16 weight producer | 17 and
+// 19 MMA issuers (one 128-column tile each, on two different SM partitions: issuing is what an MMA of this
+// size costs; 17 owns the tensor memory) | 18 producer of the small per-chunk operands (digit tile, digit sums,
+// scale and zero rows).
+// Four accumulator buffers and four operand stages in tensor memory: the round trip MMA -> epilogue -> next MMA
+// on the same buffer (about 1500 cycles) bounds the rate at one chunk per round trip / buffers.
+// A stage's 16 KiB of packed weights are released as soon as the dequant warps have read them and refilled at
+// once, so all eight stages cover the DRAM latency; the small operands (7 KiB, served by L2) stay until the
+// chunk's MMAs and epilogue are done.
+// Every wait is bounded; a wait that gives up raises the CTA's abort flag, the kernel drains, frees its tensor
+// memory and reports through g_si8_status.
+
+#include "codes.cuh"
+#include "common.cuh"
+#include "stream_layout.cuh"
+#include "tcgen05.cuh"
+#include "tma.cuh"
+
+namespace mb200 {
+namespace {
+
+using codes::kHalf;
+using stream::kGroupN;
+
+constexpr int KCH = 128;
+constexpr int NDIG = 2;
+constexpr int NCOL = 16 * NDIG;
+constexpr int THREADS = 640;
+constexpr int EPI_WARPS = 8, DQ_WARP0 = 8, DQ_WARPS = 8, PROD_WARP = 16, MMA_WARP = 17, META_WARP = 18, MMA_WARP2 = 19;
+constexpr int DBUFS = 4;
+constexpr int STAGES = 8;
+constexpr int TSTAGES = 4;
+constexpr int RAW_BYTES = KCH * kGroupN / 2;          // 16 KiB
+constexpr int ACT_BYTES = NCOL * KCH;                 // 32 digit rows x 128 k
+constexpr int OFF_ACT = RAW_BYTES;
+constexpr int OFF_S = OFF_ACT + ACT_BYTES;
+constexpr int OFF_Z = OFF_S + kGroupN * 2;
+constexpr int OFF_SA = OFF_Z + kGroupN * 2;           // 16 floats
+constexpr int STAGE_BYTES = (OFF_SA + 64 + 1023) / 1024 * 1024;
+constexpr int A_COLS = 64;                            // per operand stage: 2 tiles x 32 columns (128 k bytes)
+constexpr int DCOL = TSTAGES * A_COLS;
+constexpr int DBUF_COLS = 2 * NCOL;
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_BARS = 4 * STAGES + TSTAGES + DBUFS;
+constexpr int SMEM = 1024 + STAGES * STAGE_BYTES + NUM_BARS * 8 + 64;
+static_assert(DCOL + DBUFS * DBUF_COLS <= TMEM_COLS, "tensor memory budget");
+static_assert(SMEM <= 227 * 1024, "shared memory budget");
+static_assert(OFF_ACT % 1024 == 0, "the digit tile is a swizzled operand tile");
+
+struct I8Params {
+  const uint8_t* w;
+  void* c;
+  const void* bias;
+  float* partials;          // [CTA][2][16][256] fp32
+  int* counters;            // one per column group, zero on entry
+  const float* row_scale;   // [16]
+  const float* chunk_sums;  // [K / 128][16]
+  int M, N, K;
+  int num_groups;
+  int cps;                  // chunks per scale row
+  int kc, ng;
+  int num_ctas;
+  int split;
+  uint32_t tx_bytes;
+};
+
+__device__ int g_si8_status = 0;
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ int64_t range_start(int64_t p, int64_t U, int64_t P) { return p * U / P; }
+__device__ __forceinline__ int64_t unit_owner(int64_t u, int64_t U, int64_t P) { return ((u + 1) * P - 1) / U; }
+
+// kind::i8 instruction descriptor: s32 accumulate, signed 8-bit A and B, both K-major, M = 128, N = NCOL
+__device__ __forceinline__ constexpr uint32_t instr_desc_i8() {
+  uint32_t d = 0;
+  d |= 2u << 4;
+  d |= 1u << 7;
+  d |= 1u << 10;
+  d |= (uint32_t)(NCOL >> 3) << 17;
+  d |= (uint32_t)(128 >> 4) << 24;
+  return d;
+}
+__device__ __forceinline__ void mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t desc_lo, uint32_t desc_hi,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 d;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 d, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], d, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(desc_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_16x256b_x4(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+template <typename T>
+__device__ __forceinline__ T lds_as(uint32_t addr) {
+  const unsigned short v = (unsigned short)lds16(addr);
+  return *reinterpret_cast<const T*>(&v);
+}
+
+// Position, inside its 128-k chunk, of the digit (and weight byte) of k: the dequant thread t = k % 16 / 4 of a
+// lane pair holds, for the 16-k run j = k % 64 / 16 of 64-k block h, the word whose bytes are k % 4 = 0, 2, 1, 3;
+// that word becomes column 2 t + (j % 2) of the MMA's 32-k block 2 h + j / 2.
+__host__ __device__ inline int digit_pos(int k_local) {
+  const int h = k_local >> 6, j = (k_local >> 4) & 3, t = (k_local >> 2) & 3, e = k_local & 3;
+  const int b = ((e & 1) << 1) | (e >> 1);
+  return 32 * (2 * h + (j >> 1)) + 8 * t + 4 * (j & 1) + b;
+}
+
+// ---- activations -> digit planes -----------------------------------------------------------------------
+// One block per token row.  digits: int8 [32][K], row d * 16 + m; rows of absent tokens are zero.
+template <typename T>
+__global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a, int64_t a_stride, int M, int K,
+                                                         int8_t* __restrict__ digits, float* __restrict__ row_scale,
+                                                         float* __restrict__ chunk_sums, int* __restrict__ counters,
+                                                         int num_counters) {
+  const int m = blockIdx.x, tid = threadIdx.x;
+  pdl_release_dependents();
+  if (m == 0)
+    for (int i = tid; i < num_counters; i += 256) counters[i] = 0;
+  __shared__ float s_red[8];
+  __shared__ float s_max;
+  const int vecs = K / 8;
+  if (m >= M) {
+    for (int v = tid; v < vecs; v += 256)
+#pragma unroll
+      for (int d = 0; d < NDIG; ++d) *reinterpret_cast<uint2*>(digits + (int64_t)(d * 16 + m) * K + v * 8) = make_uint2(0, 0);
+    for (int c = tid; c < K / KCH; c += 256) chunk_sums[c * 16 + m] = 0.f;
+    if (tid == 0) row_scale[m] = 0.f;
+    return;
+  }
+  const T* row = a + (int64_t)m * a_stride;
+  float mx = 0.f;
+  for (int v = tid; v < vecs; v += 256) {
+    const uint4 q = *reinterpret_cast<const uint4*>(row + v * 8);
+    const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(to_float<T>(e[i])));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((tid & 31) == 0) s_red[tid >> 5] = mx;
+  __syncthreads();
+  if (tid == 0) {
+    float t = s_red[0];
+    for (int i = 1; i < 8; ++i) t = fmaxf(t, s_red[i]);
+    s_max = t;
+  }
+  __syncthreads();
+  mx = s_max;
+  int e = 0;
+  const bool finite = mx > 0.f && mx < 3.0e38f;
+  if (finite) {
+    (void)frexpf(mx, &e);                                   // mx = f * 2^e, f in [0.5, 1)
+    if (ldexpf(mx, 7 - e) >= 127.49f) ++e;                  // keep the first digit inside [-127, 127]
+  }
+  // x = a * 2^(7 - e), |x| < 127.5; two exact power-of-two multiplies keep the factors in range
+  const float f1 = ldexpf(1.f, (7 - e) / 2), f2 = ldexpf(1.f, (7 - e) - (7 - e) / 2);
+  if (tid == 0) row_scale[m] = finite ? ldexpf(1.f, e - 7) : 0.f;
+  // K / 8 vectors, 16 per chunk; the 256 threads of a pass cover 16 whole chunks
+  for (int v0 = 0; v0 < vecs; v0 += 256) {
+    const int v = v0 + tid;
+    float sum = 0.f;
+    if (v < vecs) {
+      const uint4 q = *reinterpret_cast<const uint4*>(row + v * 8);
+      const T* el = reinterpret_cast<const T*>(&q);
+      uint32_t out[NDIG][2] = {};
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float x = finite ? to_float<T>(el[i]) * f1 * f2 : 0.f;
+        const float d1 = rintf(x);
+        const float d2 = fminf(fmaxf(rintf((x - d1) * 256.f), -127.f), 127.f);
+        s1 += d1; s2 += d2;
+        const float dd[2] = {d1, d2};
+        const int b = (((i & 3) & 1) << 1) | ((i & 3) >> 1);   // byte of k % 4 inside its word: 0, 2, 1, 3
+#pragma unroll
+        for (int d = 0; d < NDIG; ++d) out[d][i >> 2] |= ((uint32_t)(int)dd[d] & 0xffu) << (8 * b);
+      }
+      sum = s1 + s2 * (1.f / 256.f);
+      const int chunk = v >> 4, kl = (v & 15) * 8;
+      const int p0 = digit_pos(kl), p1 = digit_pos(kl + 4);
+#pragma unroll
+      for (int d = 0; d < NDIG; ++d) {
+        int8_t* dst = digits + (int64_t)(d * 16 + m) * K + chunk * KCH;
+        *reinterpret_cast<uint32_t*>(dst + p0) = out[d][0];
+        *reinterpret_cast<uint32_t*>(dst + p1) = out[d][1];
+      }
+    }
+    // the 16 vectors of a chunk sit in 16 consecutive lanes
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (v < vecs && (tid & 15) == 0) chunk_sums[(v >> 4) * 16 + m] = sum;
+  }
+}
+
+template <typename T, int FMT>
+__global__ void __launch_bounds__(THREADS, 1)
+stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmS,
+                 const __grid_constant__ CUtensorMap tmZ, const I8Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar0 = base + STAGES * STAGE_BYTES;
+  auto full = [&](int s) { return bar0 + 8u * s; };                       // the stage's copies have landed
+  auto empty = [&](int s) { return bar0 + 8u * (STAGES + s); };           // the epilogue is done with the stage
+  auto mma_done = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };    // the chunk's MMAs have completed
+  auto a_ready = [&](int t) { return bar0 + 8u * (3 * STAGES + t); };     // operand stage written
+  auto d_free = [&](int b) { return bar0 + 8u * (3 * STAGES + TSTAGES + b); };
+  auto raw_free = [&](int s) { return bar0 + 8u * (3 * STAGES + TSTAGES + DBUFS + s); };  // packed weights read
+  const uint32_t tmem_slot = bar0 + 8u * NUM_BARS;
+
+  __shared__ int s_abort;
+  __shared__ int s_last;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full(s), 1);
+      mbar_init(empty(s), EPI_WARPS);
+      mbar_init(mma_done(s), 2);
+      mbar_init(raw_free(s), DQ_WARPS);
+    }
+    for (int t = 0; t < TSTAGES; ++t) mbar_init(a_ready(t), DQ_WARPS);
+    for (int b = 0; b < DBUFS; ++b) mbar_init(d_free(b), EPI_WARPS);
+    fence_barrier_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmS);
+    if constexpr (format_has_zp(FMT)) prefetch_tensormap(&tmZ);
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = lds32(tmem_slot);
+
+  const int64_t U = (int64_t)p.ng * p.kc;
+  int64_t u0, u1;
+  if (p.split) {
+    u0 = range_start(blockIdx.x, U, p.num_ctas);
+    u1 = range_start(blockIdx.x + 1, U, p.num_ctas);
+  } else {
+    u0 = range_start(blockIdx.x, p.ng, p.num_ctas) * p.kc;
+    u1 = range_start(blockIdx.x + 1, p.ng, p.num_ctas) * p.kc;
+  }
+  const int total = (int)(u1 - u0);
+  const int g_first = (int)(u0 / p.kc), c_first = (int)(u0 - (int64_t)g_first * p.kc);
+  pdl_release_dependents();
+
+  if (warp == PROD_WARP) {
+    // ---------------- weight producer: one linear 16 KiB copy per chunk ----------------
+    // The stage's barrier gets its whole byte count here; the small operands of the same chunk are added
+    // by the other producer, in either order.
+    if (lane == 0) {
+      const uint8_t* src = p.w + u0 * RAW_BYTES;
+      int s = 0;
+      uint32_t ph = 0;
+      for (int i = 0; i < total; ++i) {
+        if (i >= STAGES && !mbar_wait_park(raw_free(s), ph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 1); break; }
+        mbar_arrive_expect_tx(full(s), p.tx_bytes);
+        bulk_load(base + s * STAGE_BYTES, src + (int64_t)i * RAW_BYTES, RAW_BYTES, full(s));
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+      }
+    }
+  } else if (warp == META_WARP) {
+    // ---------------- producer of the digit tile, the digit sums and the scale / zero rows ----------------
+    if (lane == 0) {
+      pdl_wait_prior_grid();   // digits and sums come from the kernel in front
+      int g = g_first, c = c_first, s = 0;
+      uint32_t ph = 0;
+      for (int i = 0; i < total; ++i) {
+        if (i >= STAGES && !mbar_wait_park(empty(s), ph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 9); break; }
+        const uint32_t st = base + s * STAGE_BYTES;
+        tma_load_2d(st + OFF_ACT, &tmA, full(s), c * KCH, 0);
+        bulk_load(st + OFF_SA, p.chunk_sums + (int64_t)c * 16, 64, full(s));
+        const int srow = (p.num_groups == 1) ? 0 : c / p.cps;
+        tma_load_2d(st + OFF_S, &tmS, full(s), g * kGroupN, srow);
+        if constexpr (format_has_zp(FMT)) tma_load_2d(st + OFF_Z, &tmZ, full(s), g * kGroupN, srow);
+        if (++c == p.kc) { c = 0; ++g; }
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+      }
+    }
+  } else if (warp == MMA_WARP || warp == MMA_WARP2) {
+    // ---------------- MMA issuers: one 128-column tile each, 4 blocks of 32 k per chunk ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_i8();
+      const int tile = (warp == MMA_WARP) ? 0 : 1;
+      const uint64_t desc0 = kmajor_sw128_desc(base + OFF_ACT);
+      const uint32_t desc_lo = (uint32_t)desc0, desc_hi = (uint32_t)(desc0 >> 32);
+      int s = 0, t = 0, b = 0;
+      uint32_t ph = 0, tph = 0, bph = 0;
+      for (int i = 0; i < total; ++i) {
+        if (!mbar_wait_park(d_free(b), bph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 2); break; }
+        if (!mbar_wait_park(full(s), ph, &s_abort, 2000)) { atomicExch(&g_si8_status, 3); break; }
+        if (!mbar_wait_park(a_ready(t), tph, &s_abort, 2000)) { atomicExch(&g_si8_status, 4); break; }
+        tc_fence_after();
+        const uint32_t dlo = desc_lo + (uint32_t)((s * STAGE_BYTES) >> 4);
+        const uint32_t a_base = tmem + t * A_COLS + tile * 32;
+        const uint32_t d_addr = tmem + DCOL + b * DBUF_COLS + tile * NCOL;
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) mma_i8_ts(d_addr, a_base + kb * 8, dlo + kb * 2, desc_hi, idesc, kb == 0 ? 0u : 1u);
+        tc_commit(mma_done(s));
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+        if (++t == TSTAGES) { t = 0; tph ^= 1u; }
+        if (++b == DBUFS) { b = 0; bph ^= 1u; }
+      }
+    }
+  } else if (warp < EPI_WARPS) {
+    // ---------------- epilogue: per chunk, scale the integer sums into fp32 registers ----------------
+    const int tile = warp >> 2, quad = warp & 3;
+    const int nl = tile * 128 + quad * 32 + lane;          // column inside the group = tensor-memory lane
+    const bool hi_lane = (lane & 8) != 0;                   // second column of its packed word: byte = 16 (q - 8)
+    const float inv_alpha = hi_lane ? 1.f / 16.f : 1.f;
+    const float beta_minus_zero = (hi_lane ? 8.f : 0.f) - (FMT == kU4B8 ? 8.f : 0.f);
+    T* Cout = reinterpret_cast<T*>(p.c);
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    float acc[16];
+    bool ok = true, first_segment = true;
+    int g = g_first, c = c_first, s = 0, seg_c0 = c_first, db = 0;
+    uint32_t ph = 0;
+    for (int i = 0; i < total; ++i) {
+      const bool seg_start = (i == 0) || (c == 0);
+      const bool seg_end = (i == total - 1) || (c == p.kc - 1);
+      if (seg_start) {
+        seg_c0 = c;
+#pragma unroll
+        for (int m = 0; m < 16; ++m) acc[m] = 0.f;
+      }
+      if (ok && !mbar_wait_park(full(s), ph, &s_abort, 2000)) { atomicExch(&g_si8_status, 5); ok = false; }
+      const uint32_t st = base + s * STAGE_BYTES;
+      float sv = 0.f, zv = 0.f;
+      if (ok) {
+        sv = to_float<T>(lds_as<T>(st + OFF_S + nl * 2));
+        if constexpr (format_has_zp(FMT)) zv = to_float<T>(lds_as<T>(st + OFF_Z + nl * 2));
+      }
+      if (ok && !mbar_wait_park(mma_done(s), ph, &s_abort, 2000)) { atomicExch(&g_si8_status, 6); ok = false; }
+      int v[16];
+      if (ok) {
+        tc_fence_after();
+        const uint32_t dbase = tmem + ((uint32_t)(32 * quad) << 16) + DCOL + db * DBUF_COLS + tile * NCOL;
+        uint32_t va[16], vb[16];
+        tmem_ld16(dbase, va);
+        tmem_ld16(dbase + 16, vb);
+        tmem_ld_wait();
+        tc_fence_before();
+#pragma unroll
+        for (int m = 0; m < 16; ++m) v[m] = (int)va[m] * 256 + (int)vb[m];   // exact: |D1| < 2^22
+      }
+      // the accumulator buffer goes back before the arithmetic: the next MMA on it need not wait for that
+      __syncwarp();
+      if (lane == 0) mbar_arrive(d_free(db));
+      if (ok) {
+        const float t0 = sv * inv_alpha * (1.f / 256.f);
+        const float cfix = sv * beta_minus_zero - zv;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {   // the chunk's digit sums of the 16 rows (same for every lane)
+          const uint4 sa = lds128(st + OFF_SA + q * 16);
+          acc[4 * q + 0] = fmaf(t0, (float)v[4 * q + 0], fmaf(cfix, __uint_as_float(sa.x), acc[4 * q + 0]));
+          acc[4 * q + 1] = fmaf(t0, (float)v[4 * q + 1], fmaf(cfix, __uint_as_float(sa.y), acc[4 * q + 1]));
+          acc[4 * q + 2] = fmaf(t0, (float)v[4 * q + 2], fmaf(cfix, __uint_as_float(sa.z), acc[4 * q + 2]));
+          acc[4 * q + 3] = fmaf(t0, (float)v[4 * q + 3], fmaf(cfix, __uint_as_float(sa.w), acc[4 * q + 3]));
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty(s));
+      if (++db == DBUFS) db = 0;
+      if (seg_end) {
+        const bool whole = (seg_c0 == 0) && (c == p.kc - 1);
+        if (first_segment) pdl_wait_prior_grid();   // the row factors come from the kernel in front
+        const int n = g * kGroupN + nl;
+        if (ok && s_abort == 0) {
+          if (whole) {
+            const float bv = (bias != nullptr) ? to_float<T>(bias[bias_index(n)]) : 0.f;
+#pragma unroll
+            for (int m = 0; m < 16; ++m)
+              if (m < p.M) Cout[(int64_t)m * p.N + n] = from_float<T>(fmaf(acc[m], p.row_scale[m], bv));
+          } else {
+            float* P = p.partials + ((int64_t)blockIdx.x * 2 + (first_segment ? 0 : 1)) * (16 * kGroupN);
+#pragma unroll
+            for (int m = 0; m < 16; ++m)
+              if (m < p.M) P[m * kGroupN + nl] = acc[m] * p.row_scale[m];
+          }
+        }
+        if (!whole) {
+          // Whoever arrives last at the group's counter adds the partial sums, always in CTA order.
+          const int64_t ua = (int64_t)g * p.kc;
+          const int64_t pa = unit_owner(ua, U, p.num_ctas), pb = unit_owner(ua + p.kc - 1, U, p.num_ctas);
+          epi_barrier();
+          if (tid == 0) {
+            int last = 0;
+            if (ok && s_abort == 0) {
+              __threadfence();
+              last = (atomicAdd(p.counters + g, 1) == (int)(pb - pa)) ? 1 : 0;
+            }
+            s_last = last;
+          }
+          epi_barrier();
+          if (s_last) {
+            __threadfence();
+            const int first_slot = (range_start(pa, U, p.num_ctas) == ua) ? 0 : 1;
+            constexpr int64_t SLOT = 16 * kGroupN;
+            const float4* first = reinterpret_cast<const float4*>(p.partials + (pa * 2 + first_slot) * SLOT);
+            const int total4 = p.M * (kGroupN / 4);
+            for (int e0 = tid; e0 < total4; e0 += 256 * 4) {
+              float4 sum[4];
+#pragma unroll
+              for (int uu = 0; uu < 4; ++uu) {
+                const int e = e0 + 256 * uu;
+                sum[uu] = (e < total4) ? __ldcg(first + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+              for (int64_t q = pa + 1; q <= pb; ++q) {
+                const float4* src = reinterpret_cast<const float4*>(p.partials + (q * 2) * SLOT);
+                float4 v[4];
+#pragma unroll
+                for (int uu = 0; uu < 4; ++uu) {
+                  const int e = e0 + 256 * uu;
+                  v[uu] = (e < total4) ? __ldcg(src + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int uu = 0; uu < 4; ++uu) {
+                  sum[uu].x += v[uu].x; sum[uu].y += v[uu].y; sum[uu].z += v[uu].z; sum[uu].w += v[uu].w;
+                }
+              }
+#pragma unroll
+              for (int uu = 0; uu < 4; ++uu) {
+                const int e = e0 + 256 * uu;
+                if (e < total4) {
+                  const int m = e / (kGroupN / 4), col = (e % (kGroupN / 4)) * 4;
+                  const int nn = g * kGroupN + col;
+                  float bv[4] = {0.f, 0.f, 0.f, 0.f};
+                  if (bias != nullptr) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) bv[q] = to_float<T>(bias[bias_index(nn + q)]);
+                  }
+                  T o[4];
+                  o[0] = from_float<T>(sum[uu].x + bv[0]);
+                  o[1] = from_float<T>(sum[uu].y + bv[1]);
+                  o[2] = from_float<T>(sum[uu].z + bv[2]);
+                  o[3] = from_float<T>(sum[uu].w + bv[3]);
+                  *reinterpret_cast<uint2*>(Cout + (int64_t)m * p.N + nn) = *reinterpret_cast<const uint2*>(o);
+                }
+              }
+            }
+            if (tid == 0) p.counters[g] = 0;
+          }
+        }
+        first_segment = false;
+      }
+      if (++c == p.kc) { c = 0; ++g; }
+      if (++s == STAGES) { s = 0; ph ^= 1u; }
+    }
+  } else if (warp < DQ_WARP0 + DQ_WARPS) {
+    // ---------------- dequant: per 16-lane half, 8 packed words -> 16 byte quadruples -> one store ----------------
+    const int quad = warp & 3, tile = (warp - DQ_WARP0) >> 2;
+    const uint32_t woff = (uint32_t)((tile * 4 + quad) * 2 * 512 + lane * 16);   // half 1 is 512 bytes further on
+    const uint32_t t_lane = (uint32_t)(32 * quad) << 16;
+    bool ok = true;
+    int s = 0, t = 0, ms = 0;
+    uint32_t ph = 0, mph = 0;
+    for (int i = 0; i < total; ++i) {
+      if (ok && !mbar_wait_park(full(s), ph, &s_abort, 2000)) { atomicExch(&g_si8_status, 7); ok = false; }
+      const uint32_t st = base + s * STAGE_BYTES;
+      uint4 x[2][2] = {};
+      if (ok) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          x[half][0] = lds128(st + woff + half * 512);
+          x[half][1] = lds128(st + RAW_BYTES / 2 + woff + half * 512);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(raw_free(s));
+      // the operand stage is free once the MMAs of the chunk that used it last have completed
+      if (i >= TSTAGES) {
+        if (ok && !mbar_wait_park(mma_done(ms), mph, &s_abort, 2000)) { atomicExch(&g_si8_status, 8); ok = false; }
+        if (++ms == STAGES) { ms = 0; mph ^= 1u; }
+      }
+      if (ok) {
+        tc_fence_after();
+        // registers 4 b .. 4 b + 3 of a store: (lane g: columns 2t, 2t + 1 of 32-k block b), (lane g + 8: same)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t w[8] = {x[half][0].x, x[half][0].y, x[half][0].z, x[half][0].w,
+                                 x[half][1].x, x[half][1].y, x[half][1].z, x[half][1].w};
+          uint32_t r[16];
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            r[4 * b + 0] = w[2 * b] & 0x0f0f0f0fu;
+            r[4 * b + 1] = w[2 * b + 1] & 0x0f0f0f0fu;
+            r[4 * b + 2] = (w[2 * b] ^ 0x80808080u) & 0xf0f0f0f0u;
+            r[4 * b + 3] = (w[2 * b + 1] ^ 0x80808080u) & 0xf0f0f0f0u;
+          }
+          tmem_st_16x256b_x4(tmem + t_lane + ((uint32_t)(16 * half) << 16) + t * A_COLS + tile * 32, r);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_ready(t));
+      if (++s == STAGES) { s = 0; ph ^= 1u; }
+      if (++t == TSTAGES) t = 0;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------
+int64_t counters_bytes(int64_t n) { return ((n / kGroupN) * 4 + 255) & ~(int64_t)255; }
+int64_t partial_bytes() { return (int64_t)sm_count() * 2 * 16 * kGroupN * (int64_t)sizeof(float); }
+
+template <typename T, int FMT>
+int launch_one(const GemmArgs& g) {
+  const int64_t K = g.size_k, N = g.size_n;
+  const int m = (int)g.size_m;
+  I8Params p{};
+  p.w = reinterpret_cast<const uint8_t*>(g.bq);
+  p.c = g.c; p.bias = g.bias;
+  p.M = m; p.N = (int)N; p.K = (int)K;
+  p.num_groups = (int)g.num_groups;
+  p.kc = (int)(K / KCH);
+  p.ng = (int)(N / kGroupN);
+  p.cps = (g.num_groups == 1) ? p.kc : (int)((K / g.num_groups) / KCH);
+  const int64_t U = (int64_t)p.ng * p.kc;
+  // scratch: counters | partial sums | digit planes | row factors | per-chunk digit sums
+  uint8_t* sc = reinterpret_cast<uint8_t*>(g.scratch);
+  const int64_t cb = counters_bytes(N), pb = partial_bytes();
+  p.counters = reinterpret_cast<int*>(sc);
+  p.partials = reinterpret_cast<float*>(sc + cb);
+  int8_t* digits = reinterpret_cast<int8_t*>(sc + cb + pb);
+  float* row_scale = reinterpret_cast<float*>(digits + (int64_t)NCOL * K);
+  float* chunk_sums = row_scale + 64;
+  p.row_scale = row_scale;
+  p.chunk_sums = chunk_sums;
+  p.split = 1;
+  p.num_ctas = (int)(U < sm_count() ? U : sm_count());
+  p.tx_bytes = RAW_BYTES + ACT_BYTES + 64 + kGroupN * 2 * (format_has_zp(FMT) ? 2 : 1);
+
+  act_digits_kernel<T><<<16, 256, 0, g.stream>>>(reinterpret_cast<const T*>(g.a), g.a_stride, m, (int)K, digits,
+                                                 row_scale, chunk_sums, p.counters, p.ng);
+  MB_CUDA(cudaGetLastError());
+  count_launches(1);
+  CUtensorMap tmA, tmS, tmZ;
+  {
+    const uint64_t dims[2] = {(uint64_t)N, (uint64_t)g.num_groups};
+    const uint64_t strides[1] = {(uint64_t)N * 2};
+    const uint32_t box[2] = {kGroupN, 1};
+    if (int rc = cached_tensor_map(&tmS, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, g.scales, dims, strides, box,
+                                   CU_TENSOR_MAP_SWIZZLE_NONE))
+      return rc;
+    tmZ = tmS;
+    if (format_has_zp(FMT)) {
+      if (int rc = cached_tensor_map(&tmZ, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, g.zeros, dims, strides, box,
+                                     CU_TENSOR_MAP_SWIZZLE_NONE))
+        return rc;
+    }
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)NCOL};
+    const uint64_t strides[1] = {(uint64_t)K};
+    const uint32_t box[2] = {KCH, NCOL};
+    if (int rc = cached_tensor_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, digits, dims, strides, box,
+                                   CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  static bool attr_set[64] = {};
+  int dev = 0;
+  MB_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    MB_CUDA(cudaFuncSetAttribute(stream_i8_kernel<T, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    attr_set[dev] = true;
+  }
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.num_ctas);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = g.stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MB_CUDA(cudaLaunchKernelEx(&cfg, stream_i8_kernel<T, FMT>, tmA, tmS, tmZ, p));
+  count_launches(1);
+  return 0;
+}
+
+template <typename T>
+int launch_dtype(const GemmArgs& g) {
+  switch (g.format) {
+    case kU4B8: return launch_one<T, kU4B8>(g);
+    case kU4: return launch_one<T, kU4>(g);
+  }
+  return 1;
+}
+
+}  // namespace
+
+// counters, partial sums, then the digit planes (32 x K), the 16 row factors and K / 128 x 16 chunk sums
+int64_t gemm_stream_i8_scratch_bytes(int64_t m, int64_t n, int64_t k) {
+  if (m <= 0 || !stream::layout_accepts(k, n)) return 0;
+  return counters_bytes(n) + partial_bytes() + NCOL * k + 256 + (k / KCH) * 64;
+}
+
+bool gemm_stream_i8_accepts(const GemmArgs& g) {
+  if (g.sorted_ids != nullptr || !g.prepared) return false;
+  if (g.format != kU4B8 && g.format != kU4) return false;
+  if (g.size_m <= 0 || g.size_m > 16 || !stream::layout_accepts(g.size_k, g.size_n)) return false;
+  if (g.num_groups > 1 && (g.size_k / g.num_groups) % KCH != 0) return false;
+  if (g.global_scale != nullptr) return false;
+  return g.scratch != nullptr && g.scratch_bytes >= gemm_stream_i8_scratch_bytes(g.size_m, g.size_n, g.size_k);
+}
+
+int launch_gemm_stream_i8(const GemmArgs& g) {
+  if (g.act_dtype == MARLIN_B200_F16) return launch_dtype<__half>(g);
+  return launch_dtype<__nv_bfloat16>(g);
+}
+
+int read_stream_i8_status(int* value, bool reset) {
+  MB_CUDA(cudaMemcpyFromSymbol(value, g_si8_status, sizeof(int)));
+  if (reset && *value != 0) {
+    const int zero = 0;
+    MB_CUDA(cudaMemcpyToSymbol(g_si8_status, &zero, sizeof(int)));
+  }
+  return 0;
+}
+
+}  // namespace mb200

@@ -178,7 +178,9 @@ __device__ __forceinline__ float load_logit(const T* p) { return to_float<T>(*p)
 template <>
 __device__ __forceinline__ float load_logit<float>(const float* p) { return *p; }
 
-template <typename T>
+// SIGMOID: the scores are 1 / (1 + exp(-x)) per expert instead of the softmax over the row (topk_sigmoid of the
+// reference, csrc/moe/topk_softmax_kernels.cu:436-441); selection, bias and renormalisation are the same.
+template <typename T, bool SIGMOID>
 __global__ void __launch_bounds__(128) topk_softmax_kernel(const T* __restrict__ gating,
                                                            const float* __restrict__ bias,
                                                            float* __restrict__ weights,
@@ -206,27 +208,36 @@ __global__ void __launch_bounds__(128) topk_softmax_kernel(const T* __restrict__
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  float sum = 0.f;
+  if constexpr (SIGMOID) {
 #pragma unroll
-  for (int c = 0; c < MAX_COLS_PER_LANE / 4; ++c) {
-    if (c < chunks) {
+    for (int c = 0; c < MAX_COLS_PER_LANE / 4; ++c)
+      if (c < chunks) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float e = expf(p[c * 4 + i] - mx);
-        p[c * 4 + i] = e;
-        sum += e;
+        for (int i = 0; i < 4; ++i) p[c * 4 + i] = 1.0f / (1.0f + __expf(-p[c * 4 + i]));
+      }
+  } else {
+    float sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAX_COLS_PER_LANE / 4; ++c) {
+      if (c < chunks) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float e = expf(p[c * 4 + i] - mx);
+          p[c * 4 + i] = e;
+          sum += e;
+        }
       }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int c = 0; c < MAX_COLS_PER_LANE / 4; ++c)
+      if (c < chunks) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[c * 4 + i] *= inv;
+      }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  const float inv = 1.f / sum;
-#pragma unroll
-  for (int c = 0; c < MAX_COLS_PER_LANE / 4; ++c)
-    if (c < chunks) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) p[c * 4 + i] *= inv;
-    }
 
   // selection scores (probability + optional bias); taken entries become -inf
   float s[MAX_COLS_PER_LANE];
@@ -406,10 +417,11 @@ extern "C" int marlin_b200_moe_align_block_size(
   return 0;
 }
 
-extern "C" int marlin_b200_topk_softmax(const void* gating, int gating_dtype, const float* bias,
-                                        float* topk_weights, int32_t* topk_indices,
-                                        int32_t* token_expert_indices, int64_t num_tokens,
-                                        int64_t num_experts, int topk, int renormalize, void* stream) {
+namespace {
+template <bool SIGMOID>
+int launch_topk(const void* gating, int gating_dtype, const float* bias, float* topk_weights, int32_t* topk_indices,
+                int32_t* token_expert_indices, int64_t num_tokens, int64_t num_experts, int topk, int renormalize,
+                void* stream) {
   MB_CHECK(num_experts >= 1 && num_experts <= 128 * (MAX_COLS_PER_LANE / 4),
            "num_experts = %lld not supported (1..%d)", (long long)num_experts,
            128 * (MAX_COLS_PER_LANE / 4));
@@ -419,19 +431,19 @@ extern "C" int marlin_b200_topk_softmax(const void* gating, int gating_dtype, co
   const unsigned grid = (unsigned)((num_tokens + 3) / 4);
   switch (gating_dtype) {
     case MARLIN_B200_F16:
-      topk_softmax_kernel<__half><<<grid, 128, 0, s>>>((const __half*)gating, bias, topk_weights,
-                                                       topk_indices, token_expert_indices, num_tokens,
-                                                       (int)num_experts, topk, renormalize);
+      topk_softmax_kernel<__half, SIGMOID><<<grid, 128, 0, s>>>((const __half*)gating, bias, topk_weights,
+                                                                topk_indices, token_expert_indices, num_tokens,
+                                                                (int)num_experts, topk, renormalize);
       break;
     case MARLIN_B200_BF16:
-      topk_softmax_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(
+      topk_softmax_kernel<__nv_bfloat16, SIGMOID><<<grid, 128, 0, s>>>(
           (const __nv_bfloat16*)gating, bias, topk_weights, topk_indices, token_expert_indices,
           num_tokens, (int)num_experts, topk, renormalize);
       break;
     case 2:
-      topk_softmax_kernel<float><<<grid, 128, 0, s>>>((const float*)gating, bias, topk_weights,
-                                                      topk_indices, token_expert_indices, num_tokens,
-                                                      (int)num_experts, topk, renormalize);
+      topk_softmax_kernel<float, SIGMOID><<<grid, 128, 0, s>>>((const float*)gating, bias, topk_weights,
+                                                               topk_indices, token_expert_indices, num_tokens,
+                                                               (int)num_experts, topk, renormalize);
       break;
     default:
       MB_CHECK(false, "unsupported gating dtype %d", gating_dtype);
@@ -439,6 +451,23 @@ extern "C" int marlin_b200_topk_softmax(const void* gating, int gating_dtype, co
   MB_CUDA(cudaGetLastError());
   count_launches(1);
   return 0;
+}
+}  // namespace
+
+extern "C" int marlin_b200_topk_softmax(const void* gating, int gating_dtype, const float* bias,
+                                        float* topk_weights, int32_t* topk_indices,
+                                        int32_t* token_expert_indices, int64_t num_tokens,
+                                        int64_t num_experts, int topk, int renormalize, void* stream) {
+  return launch_topk<false>(gating, gating_dtype, bias, topk_weights, topk_indices, token_expert_indices, num_tokens,
+                            num_experts, topk, renormalize, stream);
+}
+
+extern "C" int marlin_b200_topk_sigmoid(const void* gating, int gating_dtype, const float* bias,
+                                        float* topk_weights, int32_t* topk_indices,
+                                        int32_t* token_expert_indices, int64_t num_tokens,
+                                        int64_t num_experts, int topk, int renormalize, void* stream) {
+  return launch_topk<true>(gating, gating_dtype, bias, topk_weights, topk_indices, token_expert_indices, num_tokens,
+                           num_experts, topk, renormalize, stream);
 }
 
 extern "C" int marlin_b200_silu_and_mul(const void* in, void* out, int64_t rows, int64_t inter,

@@ -103,6 +103,36 @@ __device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, v
   }
 }
 
+// Bounded wait that lets the hardware park the thread: try_wait with a suspend-time hint returns when the phase
+// completes or when the hint (nanoseconds) runs out, and a parked thread takes no issue slots.  For waits that
+// are expected to last from a fraction of a microsecond to many microseconds.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_park(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t hint_ns) {
+  if (mbar_try_wait_hint(bar, parity, hint_ns)) return true;
+  const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait_hint(bar, parity, hint_ns)) return true;
+    if (*abort_flag != 0) return false;
+    if (global_timer_ns() - t0 > 2000000000ull) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
                                             int c1) {
   asm volatile(
