@@ -227,6 +227,38 @@ int marlin_b200_topk_softmax(const void* gating, int gating_dtype, const float* 
                              int32_t* token_expert_indices, int64_t num_tokens, int64_t num_experts,
                              int topk, int renormalize, void* stream);
 
+/* The same selection on per-expert sigmoid scores 1 / (1 + exp(-x)) instead of the row softmax.  Stands in for
+ *   topk_sigmoid  csrc/moe/topk_softmax_kernels.cu:811-850 (scores: :436-441) */
+int marlin_b200_topk_sigmoid(const void* gating, int gating_dtype, const float* bias,
+                             float* topk_weights, int32_t* topk_indices,
+                             int32_t* token_expert_indices, int64_t num_tokens, int64_t num_experts,
+                             int topk, int renormalize, void* stream);
+
+/* ----------------------------------------------------------------------------------------------
+ * Block lists for tokens that are already grouped by expert (the "batched experts" format: expert e owns rows
+ * [e * max_tokens_per_batch, e * max_tokens_per_batch + expert_num_tokens[e])).  Stands in for
+ *   batched_moe_align_block_size  csrc/moe/moe_align_sum_kernels.cu:22-78,571-596
+ * sorted_token_ids int32 [num_batches * ceil(max_tokens_per_batch / block) * block]: per expert its row ids,
+ * padded to a multiple of block_size, experts back to back; everything else = num_batches *
+ * max_tokens_per_batch.  block_ids int32 [sorted_size / block]: expert of every used block, -1 elsewhere.
+ * num_tokens_post_pad int32 [1].
+ * -------------------------------------------------------------------------------------------- */
+int marlin_b200_batched_moe_align_block_size(int64_t max_tokens_per_batch, int block_size,
+                                             const int32_t* expert_num_tokens, int64_t num_batches,
+                                             int32_t* sorted_token_ids, int64_t sorted_size,
+                                             int32_t* block_ids, int64_t num_blocks,
+                                             int32_t* num_tokens_post_pad, void* stream);
+
+/* ----------------------------------------------------------------------------------------------
+ * Re-coding of 4-bit codes for the int4 -> fp8 path: per code v, v >= z ? v - z : 15 - v with z = 8
+ * (qzeros == NULL; any word count) or z = the code's AWQ zero-point (qweight int32 [rows, words_per_row],
+ * qzeros int32 [zero_rows, words_per_row], rows / zero_rows = group size, a multiple of 8).  out may be
+ * qweight itself.  Stands in for
+ *   marlin_int4_fp8_preprocess  csrc/quantization/marlin/marlin_int4_fp8_preprocess.cu:8-102
+ * -------------------------------------------------------------------------------------------- */
+int marlin_b200_int4_fp8_preprocess(const int32_t* qweight, const int32_t* qzeros, int32_t* out,
+                                    int64_t rows, int64_t words_per_row, int64_t zero_rows, void* stream);
+
 /* ----------------------------------------------------------------------------------------------
  * Glue of the two-GEMM expert layer (eager PyTorch in the reference,
  * vllm/model_executor/layers/fused_moe/fused_marlin_moe.py:161-165,379-382).

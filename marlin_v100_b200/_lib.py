@@ -37,6 +37,9 @@ SIGNATURES = {
     "marlin_b200_moe_align_block_size": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _i64, _vp, _i64,
                                                 _vp, _vp, _i64, _vp]),
     "marlin_b200_topk_softmax": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _vp]),
+    "marlin_b200_topk_sigmoid": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _vp]),
+    "marlin_b200_batched_moe_align_block_size": (_int, [_i64, _int, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp]),
+    "marlin_b200_int4_fp8_preprocess": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "marlin_b200_silu_and_mul": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
     "marlin_b200_moe_sum": (_int, [_vp, _vp, _i64, _int, _i64, _int, _vp]),
     "marlin_b200_moe_sum_rows": (_int, [_vp, _vp, _vp, _i64, _int, _i64, _int, _vp]),

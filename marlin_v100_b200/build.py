@@ -67,5 +67,52 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+TORCH_EXT_DIR = os.path.join(CSRC, "torch")
+TORCH_MODULES = {"_C": "ops_dense.cpp", "_moe_C": "ops_moe.cpp"}
+
+
+def torch_module_path(name: str) -> str:
+    return os.path.join(PKG, f"{name}.abi3.so")
+
+
+def build_torch_ops(force: bool = False) -> list[str]:
+    """The two torch extension modules `_C` / `_moe_C` (operator schemas of the reference, bodies forwarding to
+    libmarlin_b200.so).  Host C++ only: compiled with g++ against torch's headers, linked to the library by a
+    relative rpath, so the three files can be copied together into another package (`vllm/`)."""
+    from torch.utils import cpp_extension as ce
+    import sysconfig
+    build()
+    lib_dir = os.path.join(os.path.dirname(ce.__file__), "..", "lib")
+    lib_dir = os.path.abspath(lib_dir)
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    incs = [*ce.include_paths(), sysconfig.get_paths()["include"], os.path.join(cuda_home, "include"),
+            os.path.join(os.path.dirname(PKG), "include"), TORCH_EXT_DIR]
+    common = os.path.join(TORCH_EXT_DIR, "binding_common.h")
+    header = os.path.join(os.path.dirname(PKG), "include", "marlin_b200.h")
+    outs = []
+
+    def one(item):
+        name, src = item
+        src = os.path.join(TORCH_EXT_DIR, src)
+        out = torch_module_path(name)
+        if not force and not _stale(out, [src, common, header, LIB_PATH]):
+            return out
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-DPy_LIMITED_API=0x03090000",
+               f"-DTORCH_EXTENSION_NAME={name}", "-D_GLIBCXX_USE_CXX11_ABI=1",
+               *[f"-I{i}" for i in incs], src, "-o", out,
+               f"-L{LIB_DIR}", "-lmarlin_b200", f"-L{lib_dir}", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10",
+               "-lc10_cuda", "-Wl,-rpath,$ORIGIN/lib", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{lib_dir}"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"g++ failed for {src}:\n{r.stdout}\n{r.stderr}")
+        return out
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=2) as ex:
+        outs = list(ex.map(one, TORCH_MODULES.items()))
+    return outs
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose=True))
+    if "--torch-ops" in sys.argv:
+        print(build_torch_ops(force="--force" in sys.argv))

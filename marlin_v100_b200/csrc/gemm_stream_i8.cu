@@ -57,44 +57,57 @@ using stream::kGroupN;
 
 constexpr int KCH = 128;
 constexpr int NDIG = 2;
-constexpr int NCOL = 16 * NDIG;
-constexpr int THREADS = 640;
-constexpr int EPI_WARPS = 8, DQ_WARP0 = 8, DQ_WARPS = 8, PROD_WARP = 16, MMA_WARP = 17, META_WARP = 18, MMA_WARP2 = 19;
-constexpr int DBUFS = 4;
+constexpr int DQ_WARPS = 8;
 constexpr int STAGES = 8;
 constexpr int TSTAGES = 4;
 constexpr int RAW_BYTES = KCH * kGroupN / 2;          // 16 KiB
-constexpr int ACT_BYTES = NCOL * KCH;                 // 32 digit rows x 128 k
-constexpr int OFF_ACT = RAW_BYTES;
-constexpr int OFF_S = OFF_ACT + ACT_BYTES;
-constexpr int OFF_Z = OFF_S + kGroupN * 2;
-constexpr int OFF_SA = OFF_Z + kGroupN * 2;           // 16 floats
-constexpr int STAGE_BYTES = (OFF_SA + 64 + 1023) / 1024 * 1024;
 constexpr int A_COLS = 64;                            // per operand stage: 2 tiles x 32 columns (128 k bytes)
 constexpr int DCOL = TSTAGES * A_COLS;
-constexpr int DBUF_COLS = 2 * NCOL;
 constexpr int TMEM_COLS = 512;
-constexpr int NUM_BARS = 4 * STAGES + TSTAGES + DBUFS;
-constexpr int SMEM = 1024 + STAGES * STAGE_BYTES + NUM_BARS * 8 + 64;
-static_assert(DCOL + DBUFS * DBUF_COLS <= TMEM_COLS, "tensor memory budget");
-static_assert(SMEM <= 227 * 1024, "shared memory budget");
-static_assert(OFF_ACT % 1024 == 0, "the digit tile is a swizzled operand tile");
+constexpr int NUM_BARS_FIXED = 5 * STAGES + TSTAGES;
+
+// TOKH = 1: up to 8 token rows, TOKH = 2: up to 16.  An epilogue thread owns one weight column and all token
+// rows (twice the epilogue warps with 8 rows each were measured slower for 16 rows: 51 against 47 us, the
+// register budget of 28 warps makes the epilogue spill).
+template <int TOKH>
+struct Cfg {
+  static constexpr int NTOK = 8 * TOKH;
+  static constexpr int NCOL = NDIG * NTOK;                 // token columns of an MMA
+  static constexpr int EPI_WARPS = 8;
+  static constexpr int DQ_WARP0 = EPI_WARPS;
+  static constexpr int PROD_WARP = DQ_WARP0 + DQ_WARPS, MMA_WARP = PROD_WARP + 1, META_WARP = PROD_WARP + 2,
+                       MMA_WARP2 = PROD_WARP + 3;
+  static constexpr int THREADS = (PROD_WARP + 4) * 32;
+  static constexpr int ACT_BYTES = NCOL * KCH;             // digit rows x 128 k
+  static constexpr int OFF_ACT = RAW_BYTES;
+  static constexpr int OFF_S = OFF_ACT + ACT_BYTES;
+  static constexpr int OFF_Z = OFF_S + kGroupN * 2;
+  static constexpr int OFF_SA = OFF_Z + kGroupN * 2;       // NTOK floats
+  static constexpr int STAGE_BYTES = (OFF_SA + 64 + 1023) / 1024 * 1024;
+  static constexpr int DBUF_COLS = 2 * NCOL;               // two tiles
+  static constexpr int DBUFS = 256 / DBUF_COLS;            // 8 or 4 accumulator buffers
+  static constexpr int NUM_BARS = NUM_BARS_FIXED + DBUFS;
+  static constexpr int SMEM = 1024 + STAGES * STAGE_BYTES + NUM_BARS * 8 + 64;
+  static_assert(DCOL + DBUFS * DBUF_COLS <= TMEM_COLS, "tensor memory budget");
+  static_assert(SMEM <= 227 * 1024, "shared memory budget");
+  static_assert(OFF_ACT % 1024 == 0, "the digit tile is a swizzled operand tile");
+};
 
 struct I8Params {
   const uint8_t* w;
   void* c;
   const void* bias;
-  float* partials;          // [CTA][2][16][256] fp32
+  float* partials;          // [CTA][2][NTOK][256] fp32
   int* counters;            // one per column group, zero on entry
-  const float* row_scale;   // [16]
-  const float* chunk_sums;  // [K / 128][16]
+  const float* row_scale;   // [NTOK]
+  const float* chunk_sums;  // [K / 128][NTOK]
   int M, N, K;
   int num_groups;
   int cps;                  // chunks per scale row
   int kc, ng;
   int num_ctas;
   int split;
-  uint32_t tx_bytes;
+  uint32_t tx_bytes;        // bytes of the small operands of a chunk
 };
 
 __device__ int g_si8_status = 0;
@@ -103,13 +116,15 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+template <int NTHREADS>
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(NTHREADS) : "memory"); }
 __device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ int64_t range_start(int64_t p, int64_t U, int64_t P) { return p * U / P; }
 __device__ __forceinline__ int64_t unit_owner(int64_t u, int64_t U, int64_t P) { return ((u + 1) * P - 1) / U; }
 
 // kind::i8 instruction descriptor: s32 accumulate, signed 8-bit A and B, both K-major, M = 128, N = NCOL
+template <int NCOL>
 __device__ __forceinline__ constexpr uint32_t instr_desc_i8() {
   uint32_t d = 0;
   d |= 2u << 4;
@@ -150,13 +165,14 @@ __host__ __device__ inline int digit_pos(int k_local) {
 }
 
 // ---- activations -> digit planes -----------------------------------------------------------------------
-// One block per token row.  digits: int8 [32][K], row d * 16 + m; rows of absent tokens are zero.
+// One block per token row (8 or 16 blocks).  digits: int8 [2 * rows][K], row d * rows + m; rows of absent tokens
+// are zero.
 template <typename T>
 __global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a, int64_t a_stride, int M, int K,
                                                          int8_t* __restrict__ digits, float* __restrict__ row_scale,
                                                          float* __restrict__ chunk_sums, int* __restrict__ counters,
                                                          int num_counters) {
-  const int m = blockIdx.x, tid = threadIdx.x;
+  const int m = blockIdx.x, tid = threadIdx.x, ntok = gridDim.x;
   pdl_release_dependents();
   if (m == 0)
     for (int i = tid; i < num_counters; i += 256) counters[i] = 0;
@@ -166,8 +182,8 @@ __global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a
   if (m >= M) {
     for (int v = tid; v < vecs; v += 256)
 #pragma unroll
-      for (int d = 0; d < NDIG; ++d) *reinterpret_cast<uint2*>(digits + (int64_t)(d * 16 + m) * K + v * 8) = make_uint2(0, 0);
-    for (int c = tid; c < K / KCH; c += 256) chunk_sums[c * 16 + m] = 0.f;
+      for (int d = 0; d < NDIG; ++d) *reinterpret_cast<uint2*>(digits + (int64_t)(d * ntok + m) * K + v * 8) = make_uint2(0, 0);
+    for (int c = tid; c < K / KCH; c += 256) chunk_sums[c * ntok + m] = 0.f;
     if (tid == 0) row_scale[m] = 0.f;
     return;
   }
@@ -224,7 +240,7 @@ __global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a
       const int p0 = digit_pos(kl), p1 = digit_pos(kl + 4);
 #pragma unroll
       for (int d = 0; d < NDIG; ++d) {
-        int8_t* dst = digits + (int64_t)(d * 16 + m) * K + chunk * KCH;
+        int8_t* dst = digits + (int64_t)(d * ntok + m) * K + chunk * KCH;
         *reinterpret_cast<uint32_t*>(dst + p0) = out[d][0];
         *reinterpret_cast<uint32_t*>(dst + p1) = out[d][1];
       }
@@ -232,23 +248,29 @@ __global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a
     // the 16 vectors of a chunk sit in 16 consecutive lanes
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (v < vecs && (tid & 15) == 0) chunk_sums[(v >> 4) * 16 + m] = sum;
+    if (v < vecs && (tid & 15) == 0) chunk_sums[(v >> 4) * ntok + m] = sum;
   }
 }
 
-template <typename T, int FMT>
-__global__ void __launch_bounds__(THREADS, 1)
+template <typename T, int FMT, int TOKH>
+__global__ void __launch_bounds__(Cfg<TOKH>::THREADS, 1)
 stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmS,
                  const __grid_constant__ CUtensorMap tmZ, const I8Params p) {
+  using C = Cfg<TOKH>;
+  constexpr int NTOK = C::NTOK, NCOL = C::NCOL, EPI_WARPS = C::EPI_WARPS, DQ_WARP0 = C::DQ_WARP0,
+                PROD_WARP = C::PROD_WARP, MMA_WARP = C::MMA_WARP, META_WARP = C::META_WARP, MMA_WARP2 = C::MMA_WARP2,
+                STAGE_BYTES = C::STAGE_BYTES, OFF_ACT = C::OFF_ACT, OFF_S = C::OFF_S, OFF_Z = C::OFF_Z,
+                OFF_SA = C::OFF_SA, DBUF_COLS = C::DBUF_COLS, DBUFS = C::DBUFS, NUM_BARS = C::NUM_BARS;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar0 = base + STAGES * STAGE_BYTES;
-  auto full = [&](int s) { return bar0 + 8u * s; };                       // the stage's copies have landed
+  auto full = [&](int s) { return bar0 + 8u * s; };                       // the stage's packed weights have landed
+  auto fullm = [&](int s) { return bar0 + 8u * (4 * STAGES + TSTAGES + s); };  // ... its small operands
   auto empty = [&](int s) { return bar0 + 8u * (STAGES + s); };           // the epilogue is done with the stage
   auto mma_done = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };    // the chunk's MMAs have completed
   auto a_ready = [&](int t) { return bar0 + 8u * (3 * STAGES + t); };     // operand stage written
-  auto d_free = [&](int b) { return bar0 + 8u * (3 * STAGES + TSTAGES + b); };
-  auto raw_free = [&](int s) { return bar0 + 8u * (3 * STAGES + TSTAGES + DBUFS + s); };  // packed weights read
+  auto raw_free = [&](int s) { return bar0 + 8u * (3 * STAGES + TSTAGES + s); };  // packed weights read
+  auto d_free = [&](int b) { return bar0 + 8u * (NUM_BARS_FIXED + b); };
   const uint32_t tmem_slot = bar0 + 8u * NUM_BARS;
 
   __shared__ int s_abort;
@@ -258,6 +280,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     s_abort = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full(s), 1);
+      mbar_init(fullm(s), 1);
       mbar_init(empty(s), EPI_WARPS);
       mbar_init(mma_done(s), 2);
       mbar_init(raw_free(s), DQ_WARPS);
@@ -293,15 +316,13 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == PROD_WARP) {
     // ---------------- weight producer: one linear 16 KiB copy per chunk ----------------
-    // The stage's barrier gets its whole byte count here; the small operands of the same chunk are added
-    // by the other producer, in either order.
     if (lane == 0) {
       const uint8_t* src = p.w + u0 * RAW_BYTES;
       int s = 0;
       uint32_t ph = 0;
       for (int i = 0; i < total; ++i) {
         if (i >= STAGES && !mbar_wait_park(raw_free(s), ph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 1); break; }
-        mbar_arrive_expect_tx(full(s), p.tx_bytes);
+        mbar_arrive_expect_tx(full(s), RAW_BYTES);
         bulk_load(base + s * STAGE_BYTES, src + (int64_t)i * RAW_BYTES, RAW_BYTES, full(s));
         if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
@@ -315,11 +336,12 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int i = 0; i < total; ++i) {
         if (i >= STAGES && !mbar_wait_park(empty(s), ph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 9); break; }
         const uint32_t st = base + s * STAGE_BYTES;
-        tma_load_2d(st + OFF_ACT, &tmA, full(s), c * KCH, 0);
-        bulk_load(st + OFF_SA, p.chunk_sums + (int64_t)c * 16, 64, full(s));
+        mbar_arrive_expect_tx(fullm(s), p.tx_bytes);
+        tma_load_2d(st + OFF_ACT, &tmA, fullm(s), c * KCH, 0);
+        bulk_load(st + OFF_SA, p.chunk_sums + (int64_t)c * NTOK, NTOK * 4, fullm(s));
         const int srow = (p.num_groups == 1) ? 0 : c / p.cps;
-        tma_load_2d(st + OFF_S, &tmS, full(s), g * kGroupN, srow);
-        if constexpr (format_has_zp(FMT)) tma_load_2d(st + OFF_Z, &tmZ, full(s), g * kGroupN, srow);
+        tma_load_2d(st + OFF_S, &tmS, fullm(s), g * kGroupN, srow);
+        if constexpr (format_has_zp(FMT)) tma_load_2d(st + OFF_Z, &tmZ, fullm(s), g * kGroupN, srow);
         if (++c == p.kc) { c = 0; ++g; }
         if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
@@ -327,7 +349,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == MMA_WARP || warp == MMA_WARP2) {
     // ---------------- MMA issuers: one 128-column tile each, 4 blocks of 32 k per chunk ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc_i8();
+      constexpr uint32_t idesc = instr_desc_i8<NCOL>();
       const int tile = (warp == MMA_WARP) ? 0 : 1;
       const uint64_t desc0 = kmajor_sw128_desc(base + OFF_ACT);
       const uint32_t desc_lo = (uint32_t)desc0, desc_hi = (uint32_t)(desc0 >> 32);
@@ -335,7 +357,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t ph = 0, tph = 0, bph = 0;
       for (int i = 0; i < total; ++i) {
         if (!mbar_wait_park(d_free(b), bph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 2); break; }
-        if (!mbar_wait_park(full(s), ph, &s_abort, 2000)) { atomicExch(&g_si8_status, 3); break; }
+        if (!mbar_wait_park(fullm(s), ph, &s_abort, 2000)) { atomicExch(&g_si8_status, 3); break; }
         if (!mbar_wait_park(a_ready(t), tph, &s_abort, 2000)) { atomicExch(&g_si8_status, 4); break; }
         tc_fence_after();
         const uint32_t dlo = desc_lo + (uint32_t)((s * STAGE_BYTES) >> 4);
@@ -351,14 +373,16 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp < EPI_WARPS) {
     // ---------------- epilogue: per chunk, scale the integer sums into fp32 registers ----------------
-    const int tile = warp >> 2, quad = warp & 3;
+    // thread = one weight column (tensor-memory lane) x NTOK token rows
+    const int tile = (warp >> 2) & 1, quad = warp & 3;
     const int nl = tile * 128 + quad * 32 + lane;          // column inside the group = tensor-memory lane
     const bool hi_lane = (lane & 8) != 0;                   // second column of its packed word: byte = 16 (q - 8)
     const float inv_alpha = hi_lane ? 1.f / 16.f : 1.f;
     const float beta_minus_zero = (hi_lane ? 8.f : 0.f) - (FMT == kU4B8 ? 8.f : 0.f);
+    constexpr int EPI_THREADS = EPI_WARPS * 32;
     T* Cout = reinterpret_cast<T*>(p.c);
     const T* bias = reinterpret_cast<const T*>(p.bias);
-    float acc[16];
+    float acc[NTOK];
     bool ok = true, first_segment = true;
     int g = g_first, c = c_first, s = 0, seg_c0 = c_first, db = 0;
     uint32_t ph = 0;
@@ -368,9 +392,9 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (seg_start) {
         seg_c0 = c;
 #pragma unroll
-        for (int m = 0; m < 16; ++m) acc[m] = 0.f;
+        for (int m = 0; m < NTOK; ++m) acc[m] = 0.f;
       }
-      if (ok && !mbar_wait_park(full(s), ph, &s_abort, 2000)) { atomicExch(&g_si8_status, 5); ok = false; }
+      if (ok && !mbar_wait_park(fullm(s), ph, &s_abort, 2000)) { atomicExch(&g_si8_status, 5); ok = false; }
       const uint32_t st = base + s * STAGE_BYTES;
       float sv = 0.f, zv = 0.f;
       if (ok) {
@@ -378,17 +402,22 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if constexpr (format_has_zp(FMT)) zv = to_float<T>(lds_as<T>(st + OFF_Z + nl * 2));
       }
       if (ok && !mbar_wait_park(mma_done(s), ph, &s_abort, 2000)) { atomicExch(&g_si8_status, 6); ok = false; }
-      int v[16];
+      int v[NTOK];
       if (ok) {
         tc_fence_after();
         const uint32_t dbase = tmem + ((uint32_t)(32 * quad) << 16) + DCOL + db * DBUF_COLS + tile * NCOL;
-        uint32_t va[16], vb[16];
-        tmem_ld16(dbase, va);
-        tmem_ld16(dbase + 16, vb);
+        uint32_t va[NTOK], vb[NTOK];
+        if constexpr (NTOK == 8) {
+          tmem_ld8(dbase, va);
+          tmem_ld8(dbase + NTOK, vb);
+        } else {
+          tmem_ld16(dbase, va);
+          tmem_ld16(dbase + NTOK, vb);
+        }
         tmem_ld_wait();
         tc_fence_before();
 #pragma unroll
-        for (int m = 0; m < 16; ++m) v[m] = (int)va[m] * 256 + (int)vb[m];   // exact: |D1| < 2^22
+        for (int m = 0; m < NTOK; ++m) v[m] = (int)va[m] * 256 + (int)vb[m];   // exact: |D1| < 2^22
       }
       // the accumulator buffer goes back before the arithmetic: the next MMA on it need not wait for that
       __syncwarp();
@@ -397,7 +426,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const float t0 = sv * inv_alpha * (1.f / 256.f);
         const float cfix = sv * beta_minus_zero - zv;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {   // the chunk's digit sums of the 16 rows (same for every lane)
+        for (int q = 0; q < NTOK / 4; ++q) {   // the chunk's digit sums of the token rows (same for every lane)
           const uint4 sa = lds128(st + OFF_SA + q * 16);
           acc[4 * q + 0] = fmaf(t0, (float)v[4 * q + 0], fmaf(cfix, __uint_as_float(sa.x), acc[4 * q + 0]));
           acc[4 * q + 1] = fmaf(t0, (float)v[4 * q + 1], fmaf(cfix, __uint_as_float(sa.y), acc[4 * q + 1]));
@@ -416,12 +445,12 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (whole) {
             const float bv = (bias != nullptr) ? to_float<T>(bias[bias_index(n)]) : 0.f;
 #pragma unroll
-            for (int m = 0; m < 16; ++m)
+            for (int m = 0; m < NTOK; ++m)
               if (m < p.M) Cout[(int64_t)m * p.N + n] = from_float<T>(fmaf(acc[m], p.row_scale[m], bv));
           } else {
-            float* P = p.partials + ((int64_t)blockIdx.x * 2 + (first_segment ? 0 : 1)) * (16 * kGroupN);
+            float* P = p.partials + ((int64_t)blockIdx.x * 2 + (first_segment ? 0 : 1)) * (NTOK * kGroupN);
 #pragma unroll
-            for (int m = 0; m < 16; ++m)
+            for (int m = 0; m < NTOK; ++m)
               if (m < p.M) P[m * kGroupN + nl] = acc[m] * p.row_scale[m];
           }
         }
@@ -429,7 +458,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           // Whoever arrives last at the group's counter adds the partial sums, always in CTA order.
           const int64_t ua = (int64_t)g * p.kc;
           const int64_t pa = unit_owner(ua, U, p.num_ctas), pb = unit_owner(ua + p.kc - 1, U, p.num_ctas);
-          epi_barrier();
+          epi_barrier<EPI_THREADS>();
           if (tid == 0) {
             int last = 0;
             if (ok && s_abort == 0) {
@@ -438,50 +467,50 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             s_last = last;
           }
-          epi_barrier();
+          epi_barrier<EPI_THREADS>();
           if (s_last) {
             __threadfence();
             const int first_slot = (range_start(pa, U, p.num_ctas) == ua) ? 0 : 1;
-            constexpr int64_t SLOT = 16 * kGroupN;
+            constexpr int64_t SLOT = NTOK * kGroupN;
             const float4* first = reinterpret_cast<const float4*>(p.partials + (pa * 2 + first_slot) * SLOT);
             const int total4 = p.M * (kGroupN / 4);
-            for (int e0 = tid; e0 < total4; e0 += 256 * 4) {
+            for (int e0 = tid; e0 < total4; e0 += EPI_THREADS * 4) {
               float4 sum[4];
 #pragma unroll
               for (int uu = 0; uu < 4; ++uu) {
-                const int e = e0 + 256 * uu;
+                const int e = e0 + EPI_THREADS * uu;
                 sum[uu] = (e < total4) ? __ldcg(first + e) : make_float4(0.f, 0.f, 0.f, 0.f);
               }
-              for (int64_t q = pa + 1; q <= pb; ++q) {
-                const float4* src = reinterpret_cast<const float4*>(p.partials + (q * 2) * SLOT);
-                float4 v[4];
+              for (int64_t o = pa + 1; o <= pb; ++o) {
+                const float4* src = reinterpret_cast<const float4*>(p.partials + (o * 2) * SLOT);
+                float4 v4[4];
 #pragma unroll
                 for (int uu = 0; uu < 4; ++uu) {
-                  const int e = e0 + 256 * uu;
-                  v[uu] = (e < total4) ? __ldcg(src + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+                  const int e = e0 + EPI_THREADS * uu;
+                  v4[uu] = (e < total4) ? __ldcg(src + e) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
 #pragma unroll
                 for (int uu = 0; uu < 4; ++uu) {
-                  sum[uu].x += v[uu].x; sum[uu].y += v[uu].y; sum[uu].z += v[uu].z; sum[uu].w += v[uu].w;
+                  sum[uu].x += v4[uu].x; sum[uu].y += v4[uu].y; sum[uu].z += v4[uu].z; sum[uu].w += v4[uu].w;
                 }
               }
 #pragma unroll
               for (int uu = 0; uu < 4; ++uu) {
-                const int e = e0 + 256 * uu;
+                const int e = e0 + EPI_THREADS * uu;
                 if (e < total4) {
                   const int m = e / (kGroupN / 4), col = (e % (kGroupN / 4)) * 4;
                   const int nn = g * kGroupN + col;
                   float bv[4] = {0.f, 0.f, 0.f, 0.f};
                   if (bias != nullptr) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) bv[q] = to_float<T>(bias[bias_index(nn + q)]);
+                    for (int q4 = 0; q4 < 4; ++q4) bv[q4] = to_float<T>(bias[bias_index(nn + q4)]);
                   }
-                  T o[4];
-                  o[0] = from_float<T>(sum[uu].x + bv[0]);
-                  o[1] = from_float<T>(sum[uu].y + bv[1]);
-                  o[2] = from_float<T>(sum[uu].z + bv[2]);
-                  o[3] = from_float<T>(sum[uu].w + bv[3]);
-                  *reinterpret_cast<uint2*>(Cout + (int64_t)m * p.N + nn) = *reinterpret_cast<const uint2*>(o);
+                  T o4[4];
+                  o4[0] = from_float<T>(sum[uu].x + bv[0]);
+                  o4[1] = from_float<T>(sum[uu].y + bv[1]);
+                  o4[2] = from_float<T>(sum[uu].z + bv[2]);
+                  o4[3] = from_float<T>(sum[uu].w + bv[3]);
+                  *reinterpret_cast<uint2*>(Cout + (int64_t)m * p.N + nn) = *reinterpret_cast<const uint2*>(o4);
                 }
               }
             }
@@ -560,8 +589,10 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 int64_t counters_bytes(int64_t n) { return ((n / kGroupN) * 4 + 255) & ~(int64_t)255; }
 int64_t partial_bytes() { return (int64_t)sm_count() * 2 * 16 * kGroupN * (int64_t)sizeof(float); }
 
-template <typename T, int FMT>
+template <typename T, int FMT, int TOKH>
 int launch_one(const GemmArgs& g) {
+  using C = Cfg<TOKH>;
+  constexpr int NCOL = C::NCOL, NTOK = C::NTOK;
   const int64_t K = g.size_k, N = g.size_n;
   const int m = (int)g.size_m;
   I8Params p{};
@@ -579,15 +610,15 @@ int launch_one(const GemmArgs& g) {
   p.counters = reinterpret_cast<int*>(sc);
   p.partials = reinterpret_cast<float*>(sc + cb);
   int8_t* digits = reinterpret_cast<int8_t*>(sc + cb + pb);
-  float* row_scale = reinterpret_cast<float*>(digits + (int64_t)NCOL * K);
+  float* row_scale = reinterpret_cast<float*>(digits + (int64_t)32 * K);   // room for the 16-row form
   float* chunk_sums = row_scale + 64;
   p.row_scale = row_scale;
   p.chunk_sums = chunk_sums;
   p.split = 1;
   p.num_ctas = (int)(U < sm_count() ? U : sm_count());
-  p.tx_bytes = RAW_BYTES + ACT_BYTES + 64 + kGroupN * 2 * (format_has_zp(FMT) ? 2 : 1);
+  p.tx_bytes = C::ACT_BYTES + NTOK * 4 + kGroupN * 2 * (format_has_zp(FMT) ? 2 : 1);   // small operands of a chunk
 
-  act_digits_kernel<T><<<16, 256, 0, g.stream>>>(reinterpret_cast<const T*>(g.a), g.a_stride, m, (int)K, digits,
+  act_digits_kernel<T><<<NTOK, 256, 0, g.stream>>>(reinterpret_cast<const T*>(g.a), g.a_stride, m, (int)K, digits,
                                                  row_scale, chunk_sums, p.counters, p.ng);
   MB_CUDA(cudaGetLastError());
   count_launches(1);
@@ -618,7 +649,7 @@ int launch_one(const GemmArgs& g) {
   int dev = 0;
   MB_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !attr_set[dev]) {
-    MB_CUDA(cudaFuncSetAttribute(stream_i8_kernel<T, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    MB_CUDA(cudaFuncSetAttribute(stream_i8_kernel<T, FMT, TOKH>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     attr_set[dev] = true;
   }
   cudaLaunchAttribute attr[1];
@@ -626,12 +657,12 @@ int launch_one(const GemmArgs& g) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.num_ctas);
-  cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = SMEM;
+  cfg.blockDim = dim3(C::THREADS);
+  cfg.dynamicSmemBytes = C::SMEM;
   cfg.stream = g.stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  MB_CUDA(cudaLaunchKernelEx(&cfg, stream_i8_kernel<T, FMT>, tmA, tmS, tmZ, p));
+  MB_CUDA(cudaLaunchKernelEx(&cfg, stream_i8_kernel<T, FMT, TOKH>, tmA, tmS, tmZ, p));
   count_launches(1);
   return 0;
 }
@@ -639,8 +670,8 @@ int launch_one(const GemmArgs& g) {
 template <typename T>
 int launch_dtype(const GemmArgs& g) {
   switch (g.format) {
-    case kU4B8: return launch_one<T, kU4B8>(g);
-    case kU4: return launch_one<T, kU4>(g);
+    case kU4B8: return g.size_m <= 8 ? launch_one<T, kU4B8, 1>(g) : launch_one<T, kU4B8, 2>(g);
+    case kU4: return g.size_m <= 8 ? launch_one<T, kU4, 1>(g) : launch_one<T, kU4, 2>(g);
   }
   return 1;
 }
@@ -650,7 +681,7 @@ int launch_dtype(const GemmArgs& g) {
 // counters, partial sums, then the digit planes (32 x K), the 16 row factors and K / 128 x 16 chunk sums
 int64_t gemm_stream_i8_scratch_bytes(int64_t m, int64_t n, int64_t k) {
   if (m <= 0 || !stream::layout_accepts(k, n)) return 0;
-  return counters_bytes(n) + partial_bytes() + NCOL * k + 256 + (k / KCH) * 64;
+  return counters_bytes(n) + partial_bytes() + 32 * k + 256 + (k / KCH) * 64;
 }
 
 bool gemm_stream_i8_accepts(const GemmArgs& g) {

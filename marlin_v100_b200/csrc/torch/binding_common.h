@@ -5,6 +5,8 @@
 
 #include <Python.h>
 
+#include <ATen/ATen.h>
+#include <ATen/DeviceGuard.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
