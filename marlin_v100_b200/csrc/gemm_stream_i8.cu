@@ -30,11 +30,11 @@
 // scratch; the CTA that arrives last at the group's counter adds them in CTA order (no waiting; bit-identical
 // from run to run).
 //
-// Warps (640 threads, so that nothing spills): 0-7 epilogue (tile = warp / 4, 32-lane quadrant = warp % 4) |
-// 8-15 dequant (quadrant = warp % 4, tile = (warp - 8) / 4; both 16-lane halves) | 16 weight producer | 17 and
-// 19 MMA issuers (one 128-column tile each, on two different SM partitions: issuing is what an MMA of this
-// size costs; 17 owns the tensor memory) | 18 producer of the small per-chunk operands (digit tile, digit sums,
-// scale and zero rows).
+// Warps (768 threads; 80 registers each, nothing spills): 0-7 epilogue (tile = warp / 4, 32-lane quadrant =
+// warp % 4) | 8-15 dequant (quadrant = warp % 4, tile = (warp - 8) / 4; both 16-lane halves) | 16 weight
+// producer | 17 and 19 MMA issuers (one 128-column tile each, on two different SM partitions: issuing is what
+// an MMA of this size costs; 17 owns the tensor memory) | 18 producer of the small per-chunk operands (digit
+// tile, digit sums, scale and zero rows) | 20-23 cross-CTA sums of the column groups shared with other CTAs.
 // Four accumulator buffers and four operand stages in tensor memory: the round trip MMA -> epilogue -> next MMA
 // on the same buffer (about 1500 cycles) bounds the rate at one chunk per round trip / buffers.
 // A stage's 16 KiB of packed weights are released as soon as the dequant warps have read them and refilled at
@@ -64,7 +64,7 @@ constexpr int RAW_BYTES = KCH * kGroupN / 2;          // 16 KiB
 constexpr int A_COLS = 64;                            // per operand stage: 2 tiles x 32 columns (128 k bytes)
 constexpr int DCOL = TSTAGES * A_COLS;
 constexpr int TMEM_COLS = 512;
-constexpr int NUM_BARS_FIXED = 5 * STAGES + TSTAGES;
+constexpr int NUM_BARS_FIXED = 5 * STAGES + TSTAGES + 2;
 
 // TOKH = 1: up to 8 token rows, TOKH = 2: up to 16.  An epilogue thread owns one weight column and all token
 // rows (twice the epilogue warps with 8 rows each were measured slower for 16 rows: 51 against 47 us, the
@@ -77,7 +77,8 @@ struct Cfg {
   static constexpr int DQ_WARP0 = EPI_WARPS;
   static constexpr int PROD_WARP = DQ_WARP0 + DQ_WARPS, MMA_WARP = PROD_WARP + 1, META_WARP = PROD_WARP + 2,
                        MMA_WARP2 = PROD_WARP + 3;
-  static constexpr int THREADS = (PROD_WARP + 4) * 32;
+  static constexpr int REDUCE_WARP = PROD_WARP + 4;          // four warps
+  static constexpr int THREADS = (PROD_WARP + 8) * 32;
   static constexpr int ACT_BYTES = NCOL * KCH;             // digit rows x 128 k
   static constexpr int OFF_ACT = RAW_BYTES;
   static constexpr int OFF_S = OFF_ACT + ACT_BYTES;
@@ -116,8 +117,7 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-template <int NTHREADS>
-__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(NTHREADS) : "memory"); }
+__device__ __forceinline__ void reduce_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ int64_t range_start(int64_t p, int64_t U, int64_t P) { return p * U / P; }
@@ -259,6 +259,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   using C = Cfg<TOKH>;
   constexpr int NTOK = C::NTOK, NCOL = C::NCOL, EPI_WARPS = C::EPI_WARPS, DQ_WARP0 = C::DQ_WARP0,
                 PROD_WARP = C::PROD_WARP, MMA_WARP = C::MMA_WARP, META_WARP = C::META_WARP, MMA_WARP2 = C::MMA_WARP2,
+                REDUCE_WARP = C::REDUCE_WARP,
                 STAGE_BYTES = C::STAGE_BYTES, OFF_ACT = C::OFF_ACT, OFF_S = C::OFF_S, OFF_Z = C::OFF_Z,
                 OFF_SA = C::OFF_SA, DBUF_COLS = C::DBUF_COLS, DBUFS = C::DBUFS, NUM_BARS = C::NUM_BARS;
   extern __shared__ uint8_t smem_raw[];
@@ -270,13 +271,39 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   auto mma_done = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };    // the chunk's MMAs have completed
   auto a_ready = [&](int t) { return bar0 + 8u * (3 * STAGES + t); };     // operand stage written
   auto raw_free = [&](int s) { return bar0 + 8u * (3 * STAGES + TSTAGES + s); };  // packed weights read
+  auto part_ready = [&](int r) { return bar0 + 8u * (5 * STAGES + TSTAGES + r); };  // a partial sum is in scratch
   auto d_free = [&](int b) { return bar0 + 8u * (NUM_BARS_FIXED + b); };
   const uint32_t tmem_slot = bar0 + 8u * NUM_BARS;
 
   __shared__ int s_abort;
   __shared__ int s_last;
+  // The CTA visits its units in up to three runs: the part of a column group that it enters midway, the part
+  // of a group that it starts but does not finish, then its whole groups.  The groups shared with other CTAs
+  // come first so that their cross-CTA sums are formed while every CTA still streams.
+  __shared__ int s_run_g[3], s_run_c[3], s_run_len[3];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t U = (int64_t)p.ng * p.kc;
+  int64_t u0, u1;
+  if (p.split) {
+    u0 = range_start(blockIdx.x, U, p.num_ctas);
+    u1 = range_start(blockIdx.x + 1, U, p.num_ctas);
+  } else {
+    u0 = range_start(blockIdx.x, p.ng, p.num_ctas) * p.kc;
+    u1 = range_start(blockIdx.x + 1, p.ng, p.num_ctas) * p.kc;
+  }
+  const int total = (int)(u1 - u0);
   if (tid == 0) {
+    const int c0 = (int)(u0 % p.kc), e1 = (int)(u1 % p.kc);
+    const int n_head = (c0 != 0) ? ((total < p.kc - c0) ? total : p.kc - c0) : 0;
+    const int rem = total - n_head;
+    const int n_tail = (rem > 0 && e1 != 0) ? ((rem < e1) ? rem : e1) : 0;
+    const int64_t ru[3] = {u0, u1 - n_tail, u0 + n_head};
+    const int rl[3] = {n_head, n_tail, total - n_head - n_tail};
+    for (int r = 0; r < 3; ++r) {
+      s_run_g[r] = (int)(ru[r] / p.kc);
+      s_run_c[r] = (int)(ru[r] % p.kc);
+      s_run_len[r] = rl[r];
+    }
     s_abort = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full(s), 1);
@@ -286,6 +313,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(raw_free(s), DQ_WARPS);
     }
     for (int t = 0; t < TSTAGES; ++t) mbar_init(a_ready(t), DQ_WARPS);
+    for (int r = 0; r < 2; ++r) mbar_init(part_ready(r), EPI_WARPS);
     for (int b = 0; b < DBUFS; ++b) mbar_init(d_free(b), EPI_WARPS);
     fence_barrier_init();
     prefetch_tensormap(&tmA);
@@ -301,40 +329,37 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = lds32(tmem_slot);
 
-  const int64_t U = (int64_t)p.ng * p.kc;
-  int64_t u0, u1;
-  if (p.split) {
-    u0 = range_start(blockIdx.x, U, p.num_ctas);
-    u1 = range_start(blockIdx.x + 1, U, p.num_ctas);
-  } else {
-    u0 = range_start(blockIdx.x, p.ng, p.num_ctas) * p.kc;
-    u1 = range_start(blockIdx.x + 1, p.ng, p.num_ctas) * p.kc;
-  }
-  const int total = (int)(u1 - u0);
-  const int g_first = (int)(u0 / p.kc), c_first = (int)(u0 - (int64_t)g_first * p.kc);
   pdl_release_dependents();
 
   if (warp == PROD_WARP) {
     // ---------------- weight producer: one linear 16 KiB copy per chunk ----------------
     if (lane == 0) {
-      const uint8_t* src = p.w + u0 * RAW_BYTES;
-      int s = 0;
+      int s = 0, i = 0;
       uint32_t ph = 0;
-      for (int i = 0; i < total; ++i) {
-        if (i >= STAGES && !mbar_wait_park(raw_free(s), ph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 1); break; }
-        mbar_arrive_expect_tx(full(s), RAW_BYTES);
-        bulk_load(base + s * STAGE_BYTES, src + (int64_t)i * RAW_BYTES, RAW_BYTES, full(s));
-        if (++s == STAGES) { s = 0; ph ^= 1u; }
+      bool ok = true;
+      for (int r = 0; r < 3 && ok; ++r) {
+        const uint8_t* src = p.w + ((int64_t)s_run_g[r] * p.kc + s_run_c[r]) * RAW_BYTES;   // a run is linear
+        const int len = s_run_len[r];
+        for (int j = 0; j < len; ++j, ++i) {
+          if (i >= STAGES && !mbar_wait_park(raw_free(s), ph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 1); ok = false; break; }
+          mbar_arrive_expect_tx(full(s), RAW_BYTES);
+          bulk_load(base + s * STAGE_BYTES, src + (int64_t)j * RAW_BYTES, RAW_BYTES, full(s));
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
       }
     }
   } else if (warp == META_WARP) {
     // ---------------- producer of the digit tile, the digit sums and the scale / zero rows ----------------
     if (lane == 0) {
       pdl_wait_prior_grid();   // digits and sums come from the kernel in front
-      int g = g_first, c = c_first, s = 0;
+      int s = 0, i = 0;
       uint32_t ph = 0;
-      for (int i = 0; i < total; ++i) {
-        if (i >= STAGES && !mbar_wait_park(empty(s), ph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 9); break; }
+      bool ok = true;
+      for (int r = 0; r < 3 && ok; ++r) {
+      int g = s_run_g[r], c = s_run_c[r];
+      const int len = s_run_len[r];
+      for (int j = 0; j < len; ++j, ++i) {
+        if (i >= STAGES && !mbar_wait_park(empty(s), ph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 9); ok = false; break; }
         const uint32_t st = base + s * STAGE_BYTES;
         mbar_arrive_expect_tx(fullm(s), p.tx_bytes);
         tma_load_2d(st + OFF_ACT, &tmA, fullm(s), c * KCH, 0);
@@ -344,6 +369,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if constexpr (format_has_zp(FMT)) tma_load_2d(st + OFF_Z, &tmZ, fullm(s), g * kGroupN, srow);
         if (++c == p.kc) { c = 0; ++g; }
         if (++s == STAGES) { s = 0; ph ^= 1u; }
+      }
       }
     }
   } else if (warp == MMA_WARP || warp == MMA_WARP2) {
@@ -379,16 +405,18 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool hi_lane = (lane & 8) != 0;                   // second column of its packed word: byte = 16 (q - 8)
     const float inv_alpha = hi_lane ? 1.f / 16.f : 1.f;
     const float beta_minus_zero = (hi_lane ? 8.f : 0.f) - (FMT == kU4B8 ? 8.f : 0.f);
-    constexpr int EPI_THREADS = EPI_WARPS * 32;
     T* Cout = reinterpret_cast<T*>(p.c);
     const T* bias = reinterpret_cast<const T*>(p.bias);
     float acc[NTOK];
     bool ok = true, first_segment = true;
-    int g = g_first, c = c_first, s = 0, seg_c0 = c_first, db = 0;
+    int s = 0, seg_c0 = 0, db = 0;
     uint32_t ph = 0;
-    for (int i = 0; i < total; ++i) {
-      const bool seg_start = (i == 0) || (c == 0);
-      const bool seg_end = (i == total - 1) || (c == p.kc - 1);
+    for (int r = 0; r < 3; ++r) {
+    int g = s_run_g[r], c = s_run_c[r];
+    const int len = s_run_len[r];
+    for (int j = 0; j < len; ++j) {
+      const bool seg_start = (j == 0) || (c == 0);
+      const bool seg_end = (j == len - 1) || (c == p.kc - 1);
       if (seg_start) {
         seg_c0 = c;
 #pragma unroll
@@ -448,79 +476,97 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int m = 0; m < NTOK; ++m)
               if (m < p.M) Cout[(int64_t)m * p.N + n] = from_float<T>(fmaf(acc[m], p.row_scale[m], bv));
           } else {
-            float* P = p.partials + ((int64_t)blockIdx.x * 2 + (first_segment ? 0 : 1)) * (NTOK * kGroupN);
+            // slot 1: the run that starts the group (c = 0) but ends early; slot 0: a run that enters it midway
+            float* P = p.partials + ((int64_t)blockIdx.x * 2 + (seg_c0 == 0 ? 1 : 0)) * (NTOK * kGroupN);
 #pragma unroll
             for (int m = 0; m < NTOK; ++m)
               if (m < p.M) P[m * kGroupN + nl] = acc[m] * p.row_scale[m];
           }
         }
-        if (!whole) {
-          // Whoever arrives last at the group's counter adds the partial sums, always in CTA order.
-          const int64_t ua = (int64_t)g * p.kc;
-          const int64_t pa = unit_owner(ua, U, p.num_ctas), pb = unit_owner(ua + p.kc - 1, U, p.num_ctas);
-          epi_barrier<EPI_THREADS>();
-          if (tid == 0) {
-            int last = 0;
-            if (ok && s_abort == 0) {
-              __threadfence();
-              last = (atomicAdd(p.counters + g, 1) == (int)(pb - pa)) ? 1 : 0;
-            }
-            s_last = last;
-          }
-          epi_barrier<EPI_THREADS>();
-          if (s_last) {
-            __threadfence();
-            const int first_slot = (range_start(pa, U, p.num_ctas) == ua) ? 0 : 1;
-            constexpr int64_t SLOT = NTOK * kGroupN;
-            const float4* first = reinterpret_cast<const float4*>(p.partials + (pa * 2 + first_slot) * SLOT);
-            const int total4 = p.M * (kGroupN / 4);
-            for (int e0 = tid; e0 < total4; e0 += EPI_THREADS * 4) {
-              float4 sum[4];
-#pragma unroll
-              for (int uu = 0; uu < 4; ++uu) {
-                const int e = e0 + EPI_THREADS * uu;
-                sum[uu] = (e < total4) ? __ldcg(first + e) : make_float4(0.f, 0.f, 0.f, 0.f);
-              }
-              for (int64_t o = pa + 1; o <= pb; ++o) {
-                const float4* src = reinterpret_cast<const float4*>(p.partials + (o * 2) * SLOT);
-                float4 v4[4];
-#pragma unroll
-                for (int uu = 0; uu < 4; ++uu) {
-                  const int e = e0 + EPI_THREADS * uu;
-                  v4[uu] = (e < total4) ? __ldcg(src + e) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-#pragma unroll
-                for (int uu = 0; uu < 4; ++uu) {
-                  sum[uu].x += v4[uu].x; sum[uu].y += v4[uu].y; sum[uu].z += v4[uu].z; sum[uu].w += v4[uu].w;
-                }
-              }
-#pragma unroll
-              for (int uu = 0; uu < 4; ++uu) {
-                const int e = e0 + EPI_THREADS * uu;
-                if (e < total4) {
-                  const int m = e / (kGroupN / 4), col = (e % (kGroupN / 4)) * 4;
-                  const int nn = g * kGroupN + col;
-                  float bv[4] = {0.f, 0.f, 0.f, 0.f};
-                  if (bias != nullptr) {
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) bv[q4] = to_float<T>(bias[bias_index(nn + q4)]);
-                  }
-                  T o4[4];
-                  o4[0] = from_float<T>(sum[uu].x + bv[0]);
-                  o4[1] = from_float<T>(sum[uu].y + bv[1]);
-                  o4[2] = from_float<T>(sum[uu].z + bv[2]);
-                  o4[3] = from_float<T>(sum[uu].w + bv[3]);
-                  *reinterpret_cast<uint2*>(Cout + (int64_t)m * p.N + nn) = *reinterpret_cast<const uint2*>(o4);
-                }
-              }
-            }
-            if (tid == 0) p.counters[g] = 0;
-          }
+        if (!whole) {   // runs 0 and 1: the reduce warp takes it from here
+          __syncwarp();
+          if (lane == 0) mbar_arrive(part_ready(r));
         }
         first_segment = false;
       }
       if (++c == p.kc) { c = 0; ++g; }
       if (++s == STAGES) { s = 0; ph ^= 1u; }
+    }
+    }
+  } else if (warp >= REDUCE_WARP) {
+    // ---------------- cross-CTA sums of the column groups shared with other CTAs (four warps) ----------------
+    // Whoever arrives last at a group's counter adds the partial sums, always in CTA order, and writes C.
+    // Warps of their own, so that the epilogue warps (and with them the whole chunk pipeline) never wait for
+    // the fence, the atomic and the loads.
+    T* Cout = reinterpret_cast<T*>(p.c);
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    const int rt = tid - REDUCE_WARP * 32;
+    bool waited = false;
+    for (int r = 0; r < 2; ++r) {
+      if (s_run_len[r] == 0) continue;
+      const int g = s_run_g[r];
+      if (!mbar_wait_park(part_ready(r), 0, &s_abort, 2000)) { atomicExch(&g_si8_status, 10); break; }
+      if (!waited) { pdl_wait_prior_grid(); waited = true; }   // the counters were cleared by the kernel in front
+      const int64_t ua = (int64_t)g * p.kc;
+      const int64_t pa = unit_owner(ua, U, p.num_ctas), pb = unit_owner(ua + p.kc - 1, U, p.num_ctas);
+      if (rt == 0) {
+        int last = 0;
+        if (s_abort == 0) {
+          __threadfence();
+          last = (atomicAdd(p.counters + g, 1) == (int)(pb - pa)) ? 1 : 0;
+        }
+        s_last = last;
+      }
+      reduce_barrier();
+      const int last = s_last;
+      reduce_barrier();
+      if (!last) continue;
+      __threadfence();
+      constexpr int64_t SLOT = NTOK * kGroupN;
+      // the first owner holds the group's first chunks (slot 1), every other one a run from midway (slot 0)
+      const float4* first = reinterpret_cast<const float4*>(p.partials + (pa * 2 + 1) * SLOT);
+      const int total4 = p.M * (kGroupN / 4);
+      for (int e0 = rt; e0 < total4; e0 += 128 * 4) {
+        float4 sum[4];
+#pragma unroll
+        for (int uu = 0; uu < 4; ++uu) {
+          const int e = e0 + 128 * uu;
+          sum[uu] = (e < total4) ? __ldcg(first + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int64_t o = pa + 1; o <= pb; ++o) {
+          const float4* src = reinterpret_cast<const float4*>(p.partials + (o * 2) * SLOT);
+          float4 v4[4];
+#pragma unroll
+          for (int uu = 0; uu < 4; ++uu) {
+            const int e = e0 + 128 * uu;
+            v4[uu] = (e < total4) ? __ldcg(src + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int uu = 0; uu < 4; ++uu) {
+            sum[uu].x += v4[uu].x; sum[uu].y += v4[uu].y; sum[uu].z += v4[uu].z; sum[uu].w += v4[uu].w;
+          }
+        }
+#pragma unroll
+        for (int uu = 0; uu < 4; ++uu) {
+          const int e = e0 + 128 * uu;
+          if (e < total4) {
+            const int m = e / (kGroupN / 4), col = (e % (kGroupN / 4)) * 4;
+            const int nn = g * kGroupN + col;
+            float bv[4] = {0.f, 0.f, 0.f, 0.f};
+            if (bias != nullptr) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) bv[q4] = to_float<T>(bias[bias_index(nn + q4)]);
+            }
+            T o4[4];
+            o4[0] = from_float<T>(sum[uu].x + bv[0]);
+            o4[1] = from_float<T>(sum[uu].y + bv[1]);
+            o4[2] = from_float<T>(sum[uu].z + bv[2]);
+            o4[3] = from_float<T>(sum[uu].w + bv[3]);
+            *reinterpret_cast<uint2*>(Cout + (int64_t)m * p.N + nn) = *reinterpret_cast<const uint2*>(o4);
+          }
+        }
+      }
+      if (rt == 0) p.counters[g] = 0;
     }
   } else if (warp < DQ_WARP0 + DQ_WARPS) {
     // ---------------- dequant: per 16-lane half, 8 packed words -> 16 byte quadruples -> one store ----------------
