@@ -40,7 +40,8 @@ def torch_ops(tmp_path_factory):
     pkg = tmp_path_factory.mktemp("site") / "vllm"
     pkg.mkdir()
     (pkg / "__init__.py").write_text("")
-    for path in paths:
+    # the three files travel together: the modules find the library next to themselves
+    for path in [*paths, build.LIB_PATH]:
         os.symlink(path, pkg / os.path.basename(path))
     sys.path.insert(0, str(pkg.parent))
     try:
