@@ -172,19 +172,23 @@ __global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a
                                                          int8_t* __restrict__ digits, float* __restrict__ row_scale,
                                                          float* __restrict__ chunk_sums, int* __restrict__ counters,
                                                          int num_counters) {
+  // grid (token rows, parts): every block finds the maximum of its whole row (the row is small and cached), then
+  // converts its own part of the row, so that the conversion of a row is spread over several SMs
   const int m = blockIdx.x, tid = threadIdx.x, ntok = gridDim.x;
+  const int part = blockIdx.y, parts = gridDim.y;
   pdl_release_dependents();
-  if (m == 0)
+  if (m == 0 && part == 0)
     for (int i = tid; i < num_counters; i += 256) counters[i] = 0;
   __shared__ float s_red[8];
   __shared__ float s_max;
   const int vecs = K / 8;
+  const int v_begin = part * (vecs / parts), v_end = v_begin + vecs / parts;   // a multiple of 16 vectors (one chunk)
   if (m >= M) {
-    for (int v = tid; v < vecs; v += 256)
+    for (int v = v_begin + tid; v < v_end; v += 256)
 #pragma unroll
       for (int d = 0; d < NDIG; ++d) *reinterpret_cast<uint2*>(digits + (int64_t)(d * ntok + m) * K + v * 8) = make_uint2(0, 0);
-    for (int c = tid; c < K / KCH; c += 256) chunk_sums[c * ntok + m] = 0.f;
-    if (tid == 0) row_scale[m] = 0.f;
+    for (int c = v_begin / 16 + tid; c < v_end / 16; c += 256) chunk_sums[c * ntok + m] = 0.f;
+    if (tid == 0 && part == 0) row_scale[m] = 0.f;
     return;
   }
   const T* row = a + (int64_t)m * a_stride;
@@ -214,12 +218,12 @@ __global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a
   }
   // x = a * 2^(7 - e), |x| < 127.5; two exact power-of-two multiplies keep the factors in range
   const float f1 = ldexpf(1.f, (7 - e) / 2), f2 = ldexpf(1.f, (7 - e) - (7 - e) / 2);
-  if (tid == 0) row_scale[m] = finite ? ldexpf(1.f, e - 7) : 0.f;
+  if (tid == 0 && part == 0) row_scale[m] = finite ? ldexpf(1.f, e - 7) : 0.f;
   // K / 8 vectors, 16 per chunk; the 256 threads of a pass cover 16 whole chunks
-  for (int v0 = 0; v0 < vecs; v0 += 256) {
+  for (int v0 = v_begin; v0 < v_end; v0 += 256) {
     const int v = v0 + tid;
     float sum = 0.f;
-    if (v < vecs) {
+    if (v < v_end) {
       const uint4 q = *reinterpret_cast<const uint4*>(row + v * 8);
       const T* el = reinterpret_cast<const T*>(&q);
       uint32_t out[NDIG][2] = {};
@@ -248,7 +252,7 @@ __global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a
     // the 16 vectors of a chunk sit in 16 consecutive lanes
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (v < vecs && (tid & 15) == 0) chunk_sums[(v >> 4) * ntok + m] = sum;
+    if (v < v_end && (tid & 15) == 0) chunk_sums[(v >> 4) * ntok + m] = sum;
   }
 }
 
@@ -664,7 +668,9 @@ int launch_one(const GemmArgs& g) {
   p.num_ctas = (int)(U < sm_count() ? U : sm_count());
   p.tx_bytes = C::ACT_BYTES + NTOK * 4 + kGroupN * 2 * (format_has_zp(FMT) ? 2 : 1);   // small operands of a chunk
 
-  act_digits_kernel<T><<<NTOK, 256, 0, g.stream>>>(reinterpret_cast<const T*>(g.a), g.a_stride, m, (int)K, digits,
+  int parts = 1;   // as many parts per row as leave every part whole chunks and at least one pass of 256 vectors
+  while (parts < 8 && K % (KCH * parts * 2) == 0 && K / (parts * 2) >= 2048) parts *= 2;
+  act_digits_kernel<T><<<dim3(NTOK, parts), 256, 0, g.stream>>>(reinterpret_cast<const T*>(g.a), g.a_stride, m, (int)K, digits,
                                                  row_scale, chunk_sums, p.counters, p.ng);
   MB_CUDA(cudaGetLastError());
   count_launches(1);
