@@ -9,10 +9,11 @@ that is a multiple of 64 is legal).
 * `ColumnParallelMarlinLinear`: N is cut into `world` contiguous slices; every rank quantises /
   repacks its own slice (the packed layout depends on `size_n`), runs the local GEMM into its part of
   a `[world, M, N/world]` buffer and the ranks all-gather in place.
-* `ExpertParallelMoE`: tokens are data-parallel, experts are sharded contiguously.  Routing is local;
-  one all-to-all of row counts, one of rows (+ local expert id and router weight per row) to the ranks
-  that own the experts, the local fused expert layer with top_k = 1, one all-to-all back, and the
-  top-k contributions of every token are summed where the token lives.
+* `ExpertParallelMoE`: tokens are data-parallel, experts are sharded (contiguously, or by a placement
+  table that evens out the routes per rank: `balanced_expert_placement`).  Routing is local; one
+  all-to-all of row counts, one of rows (+ local expert id and router weight per row) to the ranks that
+  own the experts, the local fused expert layer with top_k = 1, one all-to-all back, and the top-k
+  contributions of every token are summed where the token lives.
 
 Both classes take a `compute` callable so the index plumbing can be exercised on CPU ranks (gloo)
 with a plain PyTorch stand-in; on GPUs the default is the CUDA library.
@@ -62,14 +63,36 @@ class ColumnParallelMarlinLinear:
 # MoE: expert parallel dispatch / combine
 # --------------------------------------------------------------------------------------------------
 
+def balanced_expert_placement(expected_load: torch.Tensor, world: int) -> torch.Tensor:
+    """Expert -> slot table (slot = rank * experts_per_rank + index on that rank) that evens out the routes per
+    rank: experts are taken in order of decreasing expected load (router statistics; any non-negative
+    weights) and each goes to the rank with the smallest load so far that still has a free slot (longest
+    processing time first).  Deterministic; returns int32 [E].  With contiguous shards a skewed router sends
+    most routes to a few ranks and the busiest rank bounds the layer."""
+    load = expected_load.detach().to(torch.float64).cpu()
+    e = load.numel()
+    if e % world:
+        raise ValueError(f"{e} experts cannot be sharded evenly over {world} ranks")
+    per = e // world
+    order = sorted(range(e), key=lambda i: (-float(load[i]), i))
+    rank_load, rank_fill = [0.0] * world, [0] * world
+    slot = torch.empty(e, dtype=torch.int32)
+    for ex in order:
+        r = min((r for r in range(world) if rank_fill[r] < per), key=lambda r: (rank_load[r], r))
+        slot[ex] = r * per + rank_fill[r]
+        rank_fill[r] += 1
+        rank_load[r] += float(load[ex])
+    return slot
+
+
 class DispatchPlan:
-    """Routes of this rank sorted by the rank that owns their expert.  The row counts per destination are
-    exchanged with an asynchronous all-to-all that is started first; `send_counts` / `recv_counts` (the
-    one host synchronisation of the layer) are only resolved when they are first read, so the caller can
-    put more device work (the row gather) in front of that synchronisation."""
+    """Routes of this rank sorted by the slot (owning rank, then expert on that rank) of their expert.  The row
+    counts per destination are exchanged with an asynchronous all-to-all that is started first;
+    `send_counts` / `recv_counts` (the one host synchronisation of the layer) are only resolved when they are
+    first read, so the caller can put more device work (the row gather) in front of that synchronisation."""
 
     def __init__(self, order, local_expert, weights, send, recv, work):
-        self.order = order                # [T*k] route indices sorted by destination rank (stable)
+        self.order = order                # [T*k] route indices sorted by destination slot (stable)
         self.local_expert = local_expert  # [T*k] expert id inside the destination rank, in `order` order
         self.weights = weights            # [T*k] router weight, in `order` order
         self._send, self._recv, self._work, self._counts = send, recv, work, None
@@ -78,7 +101,12 @@ class DispatchPlan:
         if self._counts is None:
             if self._work is not None:
                 self._work.wait()
-            self._counts = torch.stack((self._send, self._recv)).tolist()
+            both = torch.stack((self._send, self._recv)).tolist()     # [2][world][2]: (rows, invalid routes)
+            if any(c[1] for c in both[0]) or any(c[1] for c in both[1]):
+                # every rank sees the same flags (they travelled with the counts), so every rank raises here,
+                # before the row exchange: none is left waiting inside a collective
+                raise RuntimeError("expert-parallel dispatch: topk_ids holds expert ids outside [0, num_experts)")
+            self._counts = [[c[0] for c in both[0]], [c[0] for c in both[1]]]
         return self._counts
 
     @property
@@ -91,30 +119,61 @@ class DispatchPlan:
 
 
 def make_dispatch_plan(topk_ids: torch.Tensor, topk_weights: torch.Tensor, experts_per_rank: int, world: int,
-                       group=None) -> DispatchPlan:
-    """Sorts the (token, route) pairs by the rank that owns their expert and exchanges the counts."""
-    flat = topk_ids.reshape(-1).to(torch.int64)
-    dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
-    send = torch.bincount(dest, minlength=world)[:world]
+                       group=None, expert_slot: torch.Tensor | None = None) -> DispatchPlan:
+    """Sorts the (token, route) pairs by the slot of their expert and exchanges the counts.  `expert_slot`
+    (int32 [E], expert -> rank * experts_per_rank + index on the rank) defaults to contiguous shards.  On CUDA
+    the sort is the library's stable counting sort (`moe_align_block_size` with blocks of one route and the
+    slot table as its expert map): one kernel instead of a general sort."""
+    num_experts = experts_per_rank * world
+    flat = topk_ids.reshape(-1)
+    numel = flat.numel()
+    dev = flat.device
+    if flat.is_cuda:
+        from . import ops
+        if expert_slot is None:
+            expert_slot = torch.arange(num_experts, dtype=torch.int32, device=dev)
+        order32 = torch.empty(numel, dtype=torch.int32, device=dev)
+        slot_sorted = torch.empty(numel + 1, dtype=torch.int32, device=dev)
+        num_valid = torch.empty(1, dtype=torch.int32, device=dev)
+        ops.moe_align_block_size(flat.to(torch.int32).contiguous(), num_experts, 1, order32, slot_sorted, num_valid,
+                                 expert_slot)
+        slot_sorted = slot_sorted[:numel]
+        valid = slot_sorted >= 0            # routes with an id outside the table are dropped by the sort
+        order = order32.clamp_max(max(numel - 1, 0)).to(torch.int64)
+    else:
+        ids = flat.to(torch.int64)
+        ok = (ids >= 0) & (ids < num_experts)
+        slot_all = ids.clamp(0, num_experts - 1)
+        if expert_slot is not None:
+            slot_all = expert_slot.to(torch.int64)[slot_all]
+        slot_all = torch.where(ok, slot_all, torch.full_like(slot_all, num_experts))   # invalid ones sort last
+        srt = torch.sort(slot_all, stable=True)
+        order, slot_sorted = srt.indices, srt.values.to(torch.int32)
+        valid = srt.values < num_experts
+        slot_sorted = torch.where(valid, slot_sorted, torch.full_like(slot_sorted, -1))
+    dest = torch.where(valid, torch.div(slot_sorted, experts_per_rank, rounding_mode="floor"),
+                       torch.full_like(slot_sorted, world)).to(torch.int64)
+    counts = torch.bincount(dest, minlength=world + 1)
+    send = torch.stack((counts[:world], counts[world:world + 1].expand(world)), dim=1).contiguous()   # [world, 2]
     recv = torch.empty_like(send)
     work = None
     if world > 1:
         work = dist.all_to_all_single(recv, send, group=group, async_op=True)
     else:
         recv.copy_(send)
-    order = torch.sort(dest, stable=True).indices
-    local_expert = (flat - dest * experts_per_rank)[order].to(torch.int32)
+    local_expert = torch.remainder(slot_sorted.clamp_min(0), experts_per_rank).to(torch.int32)
     return DispatchPlan(order, local_expert, topk_weights.reshape(-1)[order].to(torch.float32), send, recv, work)
 
 
-def _all_to_all_rows(rows: torch.Tensor, send_counts: list[int], recv_counts: list[int], group) -> torch.Tensor:
+def _all_to_all_rows(rows: torch.Tensor, send_counts: list[int], recv_counts: list[int], group, async_op=False):
     out = torch.empty((sum(recv_counts),) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+    work = None
     if dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=recv_counts, input_split_sizes=send_counts,
-                               group=group)
+        work = dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=recv_counts,
+                                      input_split_sizes=send_counts, group=group, async_op=async_op)
     else:
-        out.copy_(rows)
-    return out
+        out.copy_(rows[:sum(send_counts)])
+    return (out, work) if async_op else out
 
 
 class ExpertParallelMoE:
@@ -123,21 +182,34 @@ class ExpertParallelMoE:
     compute(rows [R, H], local_expert int32 [R], weights fp32 [R]) -> [R, H] must return, for every
     received row, weight * expert(local_expert)(row).  The default built by `from_marlin_weights`
     runs moe_align_block_size + the two grouped GEMMs + SiLU-and-mul of the CUDA library with
-    top_k = 1."""
+    top_k = 1.
+
+    `expert_slot` (int32 [E]) places expert e at index `expert_slot[e] % experts_per_rank` of rank
+    `expert_slot[e] // experts_per_rank`; this rank's weight tensors must be stacked in that order.  Default:
+    contiguous shards.  `balanced_expert_placement` builds a table from router statistics."""
 
     def __init__(self, compute: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
-                 num_experts: int, group=None):
+                 num_experts: int, group=None, expert_slot: torch.Tensor | None = None):
         self.compute, self.num_experts, self.group = compute, num_experts, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if num_experts % self.world:
             raise ValueError(f"{num_experts} experts cannot be sharded evenly over {self.world} ranks")
         self.experts_per_rank = num_experts // self.world
+        if expert_slot is not None:
+            if sorted(expert_slot.tolist()) != list(range(num_experts)):
+                raise ValueError("expert_slot must be a permutation of range(num_experts)")
+            expert_slot = expert_slot.to(torch.int32).contiguous()
+        self.expert_slot = expert_slot
+        self.last_recv_rows = 0   # rows this rank's experts received in the last forward (load report)
+        self.record_phases = False   # CUDA events between the phases of every forward, read by phase_ms()
+        self._marks = []
 
     @classmethod
     def from_marlin_weights(cls, w13, w2, w13_scale, w2_scale, quant_type_id: int, num_experts: int, group=None,
-                            w13_zeros=None, w2_zeros=None, global_scale1=None, global_scale2=None):
-        """w13 / w2: this rank's experts ([E/world, ...]) in the packed layout of the grouped GEMM."""
+                            w13_zeros=None, w2_zeros=None, global_scale1=None, global_scale2=None,
+                            expert_slot: torch.Tensor | None = None):
+        """w13 / w2: this rank's experts ([E/world, ...], in slot order) in the packed layout of the grouped GEMM."""
         from . import fused_moe
 
         def compute(rows, local_expert, weights):
@@ -148,13 +220,35 @@ class ExpertParallelMoE:
                                               quant_type_id, global_scale1=global_scale1, global_scale2=global_scale2,
                                               w1_zeros=w13_zeros, w2_zeros=w2_zeros)
 
-        return cls(compute, num_experts, group)
+        if expert_slot is not None:
+            expert_slot = expert_slot.to(w13.device)
+        return cls(compute, num_experts, group, expert_slot)
+
+    def _mark(self, name: str):
+        if self.record_phases and torch.cuda.is_available():
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._marks.append((name, ev))
+
+    def phase_ms(self) -> dict:
+        """Device time of the phases of the last forward run with `record_phases` set (after a synchronise):
+        plan (sort, counts and their exchange, row gather), dispatch (all-to-all of rows and metadata),
+        experts (the local fused layer), combine (all-to-all back and the per-token sum)."""
+        out = {}
+        for (_, e0), (name, e1) in zip(self._marks[:-1], self._marks[1:]):
+            out[name] = e0.elapsed_time(e1)
+        return out
 
     def forward(self, hidden: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         """hidden [T, H] (this rank's tokens), topk_* [T, k] with GLOBAL expert ids -> [T, H]."""
+        self._marks = []
+        self._mark("start")
         t, h = hidden.shape
         k = topk_ids.shape[1]
-        plan = make_dispatch_plan(topk_ids, topk_weights, self.experts_per_rank, self.world, self.group)
+        slot = self.expert_slot
+        if slot is not None and slot.device != topk_ids.device:
+            slot = self.expert_slot = slot.to(topk_ids.device)
+        plan = make_dispatch_plan(topk_ids, topk_weights, self.experts_per_rank, self.world, self.group, slot)
         # everything that does not need the split sizes goes in front of the plan's host synchronisation
         token_of = torch.div(plan.order, k, rounding_mode="floor")
         send_rows = hidden.index_select(0, token_of)
@@ -164,13 +258,23 @@ class ExpertParallelMoE:
         # the contributions come back in `order` order: row inv[t * k + j] is route j of token t
         inv = torch.empty_like(plan.order)
         inv[plan.order] = torch.arange(t * k, device=plan.order.device, dtype=plan.order.dtype)
-        recv_rows = _all_to_all_rows(send_rows, plan.send_counts, plan.recv_counts, self.group)
-        recv_meta = _all_to_all_rows(meta, plan.send_counts, plan.recv_counts, self.group)
+        send_counts, recv_counts = plan.send_counts, plan.recv_counts
+        self._mark("plan")
+        # the small exchange is queued first and not waited for until the rows are in flight too
+        recv_meta, meta_work = _all_to_all_rows(meta, send_counts, recv_counts, self.group, async_op=True)
+        recv_rows = _all_to_all_rows(send_rows, send_counts, recv_counts, self.group)
+        if meta_work is not None:
+            meta_work.wait()
+        self.last_recv_rows = int(sum(recv_counts))
         recv_expert = recv_meta[:, 0].to(torch.int32)
         recv_weight = recv_meta[:, 1].contiguous()
+        self._mark("dispatch")
         out_rows = self.compute(recv_rows, recv_expert, recv_weight)
-        back = _all_to_all_rows(out_rows, plan.recv_counts, plan.send_counts, self.group)
-        return self._sum_routes(back, inv.view(t, k), hidden)
+        self._mark("experts")
+        back = _all_to_all_rows(out_rows, recv_counts, send_counts, self.group)
+        out = self._sum_routes(back, inv.view(t, k), hidden)
+        self._mark("combine")
+        return out
 
     @staticmethod
     def _sum_routes(back: torch.Tensor, inv: torch.Tensor, like: torch.Tensor) -> torch.Tensor:

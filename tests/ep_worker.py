@@ -25,23 +25,28 @@ def main():
     e, k, hdim, inter, tokens = 8 * world, 4, 256, 128, 32 * world
     g = torch.Generator().manual_seed(5)
     hidden = torch.randn(tokens, hdim, generator=g).to(dtype)
-    logits = torch.randn(tokens, e, generator=g)
+    # a skewed router: the first experts draw most routes, so contiguous shards would load rank 0 most
+    logits = torch.randn(tokens, e, generator=g) + torch.linspace(2.0, -2.0, e)
     w13 = util.make_experts(e, hdim, 2 * inter, fmt, dtype, seed=6, scale=0.05)
     w2 = util.make_experts(e, inter, hdim, fmt, dtype, seed=7, scale=0.05)
     per = e // world
-    sl_e = slice(rank * per, (rank + 1) * per)
+    # experts placed by expected load; this rank stacks the experts of its slots in slot order
+    slot = parallel.balanced_expert_placement(torch.softmax(logits, -1).sum(0), world)
+    sl_e = torch.argsort(slot)[rank * per:(rank + 1) * per]
     tok = tokens // world
     sl_t = slice(rank * tok, (rank + 1) * tok)
     dev = "cuda"
     layer = parallel.ExpertParallelMoE.from_marlin_weights(
         w13.packed[sl_e].to(dev), w2.packed[sl_e].to(dev), w13.scales[sl_e].to(dev), w2.scales[sl_e].to(dev),
-        w13.type_id, e)
+        w13.type_id, e, expert_slot=slot)
     tw, ids, _ = fused_moe.fused_topk(logits[sl_t].to(dev), k, True)
     out = layer.forward(hidden[sl_t].to(dev), tw, ids)
     torch.cuda.synchronize()
     rtw, rids, _ = mo.topk_softmax_reference(logits, k, True)
     ref = mo.moe_reference(hidden, w13.deq, w2.deq, rtw, rids, round_dtype=dtype)[sl_t]
     ok = torch.equal(ids.cpu(), rids[sl_t]) and mo.within_tolerance(out.cpu(), ref)
+    # the placement must spread the routes: no rank receives more than 1.5x its even share
+    ok = ok and layer.last_recv_rows <= 1.5 * tokens * k / world
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:

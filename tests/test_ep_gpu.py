@@ -1,6 +1,7 @@
 """Expert-parallel layer on GPUs: world size 1 must equal the plain fused layer; with two or more
 GPUs a torchrun job checks the NCCL dispatch / combine against the CPU oracle."""
 import os
+import socket
 import subprocess
 import sys
 
@@ -36,8 +37,11 @@ def test_world1_equals_fused_layer():
 def test_multi_gpu_dispatch_combine():
     n = min(torch.cuda.device_count(), 4)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-                        "--master-addr", "127.0.0.1", "--master-port", "29541",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port),
                         os.path.join(ROOT, "tests", "ep_worker.py")], capture_output=True, text=True, env=env,
                        timeout=600)
     assert r.returncode == 0 and "EP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

@@ -43,7 +43,10 @@ def _worker(rank, world, port, results):
     try:
         hidden, experts, w, ids = _problem()
         per_rank = experts.shape[0] // world
-        mine = experts[rank * per_rank:(rank + 1) * per_rank]
+        # experts placed by a load table; this rank stacks the experts of its slots in slot order
+        slot = parallel.balanced_expert_placement(torch.tensor([9.0, 8, 1, 1, 1, 1, 1, 1]), world)
+        expert_of_slot = torch.argsort(slot)
+        mine = experts[expert_of_slot[rank * per_rank:(rank + 1) * per_rank]]
 
         def compute(rows, local_expert, weights):
             out = torch.empty_like(rows)
@@ -51,12 +54,21 @@ def _worker(rank, world, port, results):
                 out[i] = weights[i] * torch.tanh(rows[i] @ mine[int(local_expert[i])])
             return out
 
-        layer = parallel.ExpertParallelMoE(compute, experts.shape[0])
+        layer = parallel.ExpertParallelMoE(compute, experts.shape[0], expert_slot=slot)
         tok = hidden.shape[0] // world
         sl = slice(rank * tok, (rank + 1) * tok)
         out = layer.forward(hidden[sl], w[sl], ids[sl])
         ref = _reference(hidden, experts, w, ids)[sl]
         ok_moe = torch.allclose(out, ref, atol=1e-5)
+        # an expert id outside the table on ONE rank: both ranks raise before the row exchange
+        bad = ids[sl].clone()
+        if rank == 1:
+            bad[0, 0] = experts.shape[0]
+        try:
+            layer.forward(hidden[sl], w[sl], bad)
+            ok_moe = False
+        except RuntimeError as err:
+            ok_moe = ok_moe and "outside" in str(err)
 
         # dense column split
         g = torch.Generator().manual_seed(3)
@@ -94,11 +106,37 @@ def test_single_process_paths():
     assert parallel.column_slice(512, 1, 4) == (128, 256)
 
 
-def test_dispatch_plan_orders_routes_by_owner():
+def test_dispatch_plan_orders_routes_by_slot():
     ids = torch.tensor([[5, 0], [2, 7], [1, 6]], dtype=torch.int32)
     w = torch.arange(6, dtype=torch.float32).reshape(3, 2)
-    plan = parallel.make_dispatch_plan(ids, w, experts_per_rank=4, world=1)
-    # owners: [1,0],[0,1],[0,1] -> stable order of owner-0 routes first
-    assert plan.order.tolist() == [1, 2, 4, 0, 3, 5]
-    assert plan.local_expert.tolist() == [0, 2, 1, 1, 3, 2]
-    assert plan.weights.tolist() == [1.0, 2.0, 4.0, 0.0, 3.0, 5.0]
+    plan = parallel.make_dispatch_plan(ids, w, experts_per_rank=8, world=1)
+    assert plan.order.tolist() == [1, 4, 2, 0, 5, 3]
+    assert plan.local_expert.tolist() == [0, 1, 2, 5, 6, 7]
+    assert plan.weights.tolist() == [1.0, 4.0, 2.0, 0.0, 5.0, 3.0]
+    assert plan.send_counts == [6] and plan.recv_counts == [6]
+    # a placement table: expert e lives in slot 7 - e
+    slot = torch.arange(7, -1, -1, dtype=torch.int32)
+    plan = parallel.make_dispatch_plan(ids, w, experts_per_rank=8, world=1, expert_slot=slot)
+    assert plan.order.tolist() == [3, 5, 0, 2, 4, 1]
+    assert plan.local_expert.tolist() == [0, 1, 2, 5, 6, 7]
+
+
+def test_dispatch_plan_rejects_ids_outside_the_table():
+    w = torch.ones(2, 2)
+    for bad in (8, -1):
+        plan = parallel.make_dispatch_plan(torch.tensor([[0, bad], [1, 2]], dtype=torch.int32), w, 8, 1)
+        with pytest.raises(RuntimeError, match="outside"):
+            plan.send_counts
+
+
+def test_balanced_expert_placement():
+    load = torch.tensor([10.0, 9.0, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0])
+    slot = parallel.balanced_expert_placement(load, 2)
+    assert sorted(slot.tolist()) == list(range(8))
+    per_rank = [sum(float(load[e]) for e in range(8) if int(slot[e]) // 4 == r) for r in range(2)]
+    assert max(per_rank) <= 13.0          # contiguous shards would put 21 of 25 on rank 0
+    assert int(slot[0]) // 4 != int(slot[1]) // 4
+    with pytest.raises(ValueError):
+        parallel.balanced_expert_placement(load, 3)
+    with pytest.raises(ValueError):
+        parallel.ExpertParallelMoE(lambda *a: None, 8, expert_slot=torch.zeros(8, dtype=torch.int32))
