@@ -276,6 +276,12 @@ def fp8_scale_exponent_bias(dtype: torch.dtype) -> int:
     return 8 if dtype == torch.float16 else 120
 
 
+def fp8_fuse_exponent_bias(scales: torch.Tensor) -> torch.Tensor:
+    """Boundary form of fp8 scales: scale * 2^bias in the scales' own dtype
+    (vllm/model_executor/layers/quantization/utils/marlin_utils_fp8.py:28-39)."""
+    return scales * (torch.ones_like(scales) * 2) ** fp8_scale_exponent_bias(scales.dtype)
+
+
 def quantize_fp8(weight: torch.Tensor, group_size: int):
     """fp8-e4m3: s = amax / 448 (tests/helpers.py:890-911).  Returns (raw bytes [K,N] int32,
     boundary scales [G,N] = s * 2^bias in weight dtype, plain scales fp32)."""
@@ -335,6 +341,18 @@ def nvfp4_encode_scales(fp8_scales: torch.Tensor, a_dtype: torch.dtype, scale_fa
         s = (s.float() * scale_factor).to(torch.float16)
     bits = ((s * 128.0).view(torch.int16) << 1).view(torch.float8_e4m3fn)
     return bits[:, 1::2].contiguous(), scale_factor
+
+
+def nvfp4_process_global_scale(global_scale: torch.Tensor, a_dtype: torch.dtype) -> torch.Tensor:
+    """Boundary form of the nvfp4 global scale: g * 2^(bias - 7) (marlin_utils_fp4.py:132-144)."""
+    return global_scale * (2.0 ** (nvfp4_exponent_bias(a_dtype) - 7))
+
+
+def mxfp4_encode_scales(scales: torch.Tensor) -> torch.Tensor:
+    """The reference's Marlin-side form of mxfp4 scales for 16-bit activations: [0,2,1,3] interleave per 4
+    along N, stored as e8m0 (marlin_utils_fp4.py:115-129)."""
+    s = scales.reshape(-1, 4)[:, [0, 2, 1, 3]].reshape(scales.shape)
+    return s.to(torch.float8_e8m0fnu)
 
 
 def nvfp4_decode_scales(scale_bytes: torch.Tensor) -> torch.Tensor:
@@ -551,6 +569,15 @@ def max_abs_err_frac(y: torch.Tensor, ref: torch.Tensor) -> float:
     """max|y - ref| / max|ref|."""
     y, ref = y.to(torch.float32), ref.to(torch.float32)
     return float((y - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+
+
+def mean_elem_rel_err(y: torch.Tensor, ref: torch.Tensor, eps: float | None = None) -> float:
+    """mean(|y - ref| / max(|ref|, eps)): the per-element form.  eps defaults to mean|ref|, so an element
+    smaller than the typical output is measured against the typical output, not against itself."""
+    y, ref = y.to(torch.float32), ref.to(torch.float32)
+    if eps is None:
+        eps = float(ref.abs().mean().clamp_min(1e-30))
+    return float(((y - ref).abs() / ref.abs().clamp_min(eps)).mean())
 
 
 def within_tolerance(y: torch.Tensor, ref: torch.Tensor, mean_tol: float = 1e-2,

@@ -152,3 +152,38 @@ def test_align_expert_map_and_empty_experts():
     assert int(t) == 6
     assert s[:6].tolist() == [1, 6, 4, 5, 0, 3]
     assert e[:3].tolist() == [0, 1, 2]
+
+
+# --- scale encoders of the fp4 / fp8 paths, fp16 and bf16, against the reference's own functions --------
+S = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_scale_encoders.npz"))
+
+
+def TS(name, dtype=None):
+    t = torch.from_numpy(S[name].copy())
+    return t if dtype is None else t.view(dtype)
+
+
+@pytest.mark.parametrize("tag", ["wide", "narrow"])
+@pytest.mark.parametrize("dn,dt", [("f16", torch.float16), ("bf16", torch.bfloat16)])
+def test_nvfp4_scale_encoder_matches_reference(tag, dn, dt):
+    s = TS(f"nvfp4_{tag}_in", torch.float8_e4m3fn)
+    enc, sf = mo.nvfp4_encode_scales(s.to(dt), dt)
+    assert sf == float(S[f"nvfp4_{tag}_{dn}_sf"][0])
+    assert torch.equal(enc.view(torch.uint8), TS(f"nvfp4_{tag}_{dn}_enc"))
+    if tag == "wide":
+        assert (sf > 1.0) == (dt == torch.bfloat16)   # only the bf16 path rescales small scales
+
+
+@pytest.mark.parametrize("dn,dt", [("f16", torch.float16), ("bf16", torch.bfloat16)])
+def test_global_scale_and_fp8_bias_match_reference(dn, dt):
+    assert torch.equal(mo.nvfp4_process_global_scale(TS("nvfp4_global_in"), dt), TS(f"nvfp4_global_{dn}"))
+    sc = TS(f"fp8_scale_{dn}_in", dt if dt == torch.float16 else None)
+    exp = TS(f"fp8_scale_{dn}_out", dt if dt == torch.float16 else None)
+    if dt == torch.bfloat16:
+        sc, exp = sc.view(torch.bfloat16), exp.view(torch.bfloat16)
+    assert torch.equal(mo.fp8_fuse_exponent_bias(sc), exp)
+
+
+def test_mxfp4_scale_encoder_matches_reference():
+    enc = mo.mxfp4_encode_scales(TS("mxfp4_in").to(torch.bfloat16))
+    assert torch.equal(enc.view(torch.uint8), TS("mxfp4_enc"))

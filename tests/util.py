@@ -37,8 +37,10 @@ class QuantWeight:
     extra: dict = field(default_factory=dict)
 
 
-def quantize(weight: torch.Tensor, fmt: str, group_size: int | None = None, want_deq: bool = True) -> QuantWeight:
-    """Quantise ``weight`` [K, N] (fp16/bf16, CPU) to the tensors the GEMM op receives."""
+def quantize(weight: torch.Tensor, fmt: str, group_size: int | None = None, want_deq: bool = True,
+             pack: bool = True) -> QuantWeight:
+    """Quantise ``weight`` [K, N] (fp16/bf16, CPU) to the tensors the GEMM op receives.  With ``pack=False``
+    the codes stay in ``extra["q"]`` and ``packed`` is None (the caller repacks them on the GPU)."""
     k, n = weight.shape
     gs = default_group(fmt, group_size)
     zeros = gscale = None
@@ -59,11 +61,11 @@ def quantize(weight: torch.Tensor, fmt: str, group_size: int | None = None, want
         q, scales = mo.quantize_mxfp4(weight)
     else:
         raise ValueError(fmt)
-    packed = mo.marlin_pack(q, bits)
+    packed = mo.marlin_pack(q, bits) if pack else None
     qw = QuantWeight(fmt, k, n, gs, TYPE_IDS[fmt], packed, scales.contiguous(), zeros, gscale)
     qw.extra["q"] = q
     qw.extra["bits"] = bits
-    if want_deq:
+    if want_deq and pack:
         qw.deq = mo.dequantize(packed, scales, k, n, qw.type_id, zeros=zeros, global_scale=gscale,
                                out_dtype=weight.dtype)
     return qw
