@@ -275,6 +275,62 @@ int marlin_b200_moe_sum(const void* in, void* out, int64_t tokens, int top_k, in
 int marlin_b200_moe_sum_rows(const void* in, const int32_t* rows, void* out, int64_t tokens, int top_k,
                              int64_t hidden, int act_dtype, void* stream);
 
+/* ----------------------------------------------------------------------------------------------
+ * Multi-GPU steps over peer-mapped memory.  No counterpart in the reference, whose distributed layer is a
+ * world-size-1 stub (vllm/distributed/__init__.py:4-25); the layouts stand on its `expert_map` hook
+ * (fused_marlin_moe.py:170-171) and on output columns being independent (marlin.cu:356-359).
+ *
+ * Every rank (one process per GPU of one node) allocates an arena, exports it, and opens the arenas of
+ * all other ranks; `arenas[r]` is rank r's arena as mapped in THIS process (arenas[rank] is the local
+ * allocation).  The first marlin_b200_peer_header_bytes() bytes of an arena belong to the library (step
+ * counter, status, flags, count tables); the caller lays out the rest, identically on every rank.  The
+ * kernels move data with plain loads and stores to peer addresses and order it with flags; every wait is
+ * bounded (two seconds), after which the arena's status word is set and the kernels of that arena stop
+ * moving data: read it with marlin_b200_peer_status (0 = fine, 1 + phase = a wait of that phase gave up,
+ * 16 = receive capacity exceeded).  All ranks must issue the same sequence of steps on an arena.
+ * -------------------------------------------------------------------------------------------- */
+int marlin_b200_peer_header_bytes(void);
+int marlin_b200_peer_alloc(int64_t bytes, void** ptr);            /* zero-filled device memory           */
+int marlin_b200_peer_free(void* ptr);
+int marlin_b200_peer_export(void* ptr, void* handle64);           /* 64-byte handle for other processes  */
+int marlin_b200_peer_open(const void* handle64, void** ptr);      /* map another rank's arena            */
+int marlin_b200_peer_close(void* ptr);
+int marlin_b200_peer_status(const void* arena, int* status, int* steps_done);   /* synchronous read     */
+int marlin_b200_peer_host_word_alloc(void** host_ptr, void** device_ptr);       /* 64 mapped host bytes */
+int marlin_b200_peer_host_word_free(void* host_ptr);
+
+/* Column-parallel dense layer: every rank's `src` (bytes_per_rank bytes, a multiple of 16) gathered into
+ * `out`.  slice_rows == 0: out is [world][bytes_per_rank].  slice_rows == M: src is an [M, cols] row block and
+ * out is [M, world * cols] (rank r's columns at r * cols).  The arena holds two gather buffers of
+ * world * bytes_per_rank bytes at buffer_offset.  No host synchronisation: the call can be captured. */
+int marlin_b200_peer_allgather(const void* const* arenas, int rank, int world, const void* src,
+                               int64_t bytes_per_rank, int64_t buffer_offset, void* out, int64_t slice_rows,
+                               void* stream);
+
+/* Expert-parallel layer, one step = plan, dispatch, [poll_rows on the host], wait(2), the expert layer on
+ * the received rows, signal(3), combine.
+ *   layout[6] = arena offsets of {received rows, int32 expert index per row, float router weight per row,
+ *               expert outputs}, row capacity, bytes per row (hidden * 2).
+ *   slot_sorted / order: the expert_ids / sorted_token_ids outputs of marlin_b200_moe_align_block_size with
+ *               block_size 1 and the expert -> slot table as expert_map (slot = rank * experts_per_rank +
+ *               index on that rank; routes with ids outside the table sit at the end as -1).
+ *   position_of_route: int32 [tokens * top_k] scratch written by dispatch and read by combine.
+ *   poll_rows returns the rows this rank received, the number of routes with invalid ids on any rank (the
+ *               caller then issues signal + combine with skip = 1 and raises on every rank) and the status. */
+int marlin_b200_ep_plan(const void* const* arenas, int rank, int world, const int32_t* slot_sorted, int64_t numel,
+                        int experts_per_rank, void* stream);
+int marlin_b200_ep_dispatch(const void* const* arenas, int rank, int world, const int64_t* layout,
+                            const void* hidden, const int32_t* order, const int32_t* slot_sorted,
+                            const float* topk_weights, int32_t* position_of_route, int top_k,
+                            int experts_per_rank, void* host_word_device, void* stream);
+int marlin_b200_ep_poll_rows(const void* host_word, int step, int timeout_ms, int64_t* rows,
+                             int* invalid_routes, int* status);
+int marlin_b200_ep_wait(const void* const* arenas, int rank, int world, int phase, void* stream);
+int marlin_b200_ep_signal(const void* const* arenas, int rank, int world, int phase, void* stream);
+int marlin_b200_ep_combine(const void* const* arenas, int rank, int world, const int64_t* layout,
+                           const int32_t* position_of_route, int top_k, int64_t tokens, void* out,
+                           int act_dtype, int skip, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

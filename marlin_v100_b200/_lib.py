@@ -43,6 +43,22 @@ SIGNATURES = {
     "marlin_b200_silu_and_mul": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
     "marlin_b200_moe_sum": (_int, [_vp, _vp, _i64, _int, _i64, _int, _vp]),
     "marlin_b200_moe_sum_rows": (_int, [_vp, _vp, _vp, _i64, _int, _i64, _int, _vp]),
+    "marlin_b200_peer_header_bytes": (_int, []),
+    "marlin_b200_peer_alloc": (_int, [_i64, _vp]),
+    "marlin_b200_peer_free": (_int, [_vp]),
+    "marlin_b200_peer_export": (_int, [_vp, _vp]),
+    "marlin_b200_peer_open": (_int, [_vp, _vp]),
+    "marlin_b200_peer_close": (_int, [_vp]),
+    "marlin_b200_peer_status": (_int, [_vp, _vp, _vp]),
+    "marlin_b200_peer_host_word_alloc": (_int, [_vp, _vp]),
+    "marlin_b200_peer_host_word_free": (_int, [_vp]),
+    "marlin_b200_peer_allgather": (_int, [_vp, _int, _int, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "marlin_b200_ep_plan": (_int, [_vp, _int, _int, _vp, _i64, _int, _vp]),
+    "marlin_b200_ep_dispatch": (_int, [_vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp, _vp]),
+    "marlin_b200_ep_poll_rows": (_int, [_vp, _int, _int, _vp, _vp, _vp]),
+    "marlin_b200_ep_wait": (_int, [_vp, _int, _int, _int, _vp]),
+    "marlin_b200_ep_signal": (_int, [_vp, _int, _int, _int, _vp]),
+    "marlin_b200_ep_combine": (_int, [_vp, _int, _int, _vp, _vp, _int, _i64, _vp, _int, _int, _vp]),
 }
 
 FMT_PREPARED = 0x100  # MARLIN_B200_FMT_PREPARED

@@ -95,11 +95,21 @@ def fused_marlin_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Te
                               True, is_w1_zp_float)
     act = torch.empty((m * topk, n), dtype=hidden_states.dtype, device=dev)
     ops.silu_and_mul(act, c1)
-    c3 = alloc((m * topk, k), dtype=hidden_states.dtype, device=dev)
+    if topk == 1:
+        # one route per row: the second GEMM writes the result itself, there is nothing to sum
+        if output is None:
+            output = hidden_states if inplace else torch.empty_like(hidden_states)
+        if zero_fill:
+            output.zero_()
+        c3 = output
+    else:
+        c3 = alloc((m * topk, k), dtype=hidden_states.dtype, device=dev)
     ops.moe_wna16_marlin_gemm(act, c3, w2, bias2, w2_scale, None, global_scale2, w2_zeros, None, None,
                               workspace, sorted_ids, expert_ids, num_post, flat_w, block_size_m, 1,
                               not apply_router_weight_on_input, quant_type_id, m * topk, k, n, True, False,
                               True, is_w2_zp_float)
+    if topk == 1:
+        return output
     if output is None:
         output = hidden_states if inplace else torch.empty_like(hidden_states)
     ops.moe_sum(c3.view(m, topk, k), output)

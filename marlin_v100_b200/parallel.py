@@ -17,13 +17,109 @@ that is a multiple of 64 is legal).
 
 Both classes take a `compute` callable so the index plumbing can be exercised on CPU ranks (gloo)
 with a plain PyTorch stand-in; on GPUs the default is the CUDA library.
+
+Transport.  The portable form of both layers moves data with `torch.distributed` collectives (NCCL on
+GPUs, gloo on CPU ranks).  On the GPUs of one node both layers can instead use the library's own kernels
+over peer-mapped memory (`PeerArena`, `use_peer_memory=True`): the all-gather of the dense layer is one
+kernel that stores this rank's slice into every rank's buffer, and the expert-parallel layer stores every
+route's row straight into the owning rank's receive buffer and reads the contributions back with peer
+loads, with no collective library call and no stream synchronisation in the step.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Callable
 
 import torch
 import torch.distributed as dist
+
+
+# --------------------------------------------------------------------------------------------------
+# peer-mapped memory of the ranks of one node
+# --------------------------------------------------------------------------------------------------
+
+class _DeviceBytes:
+    """Lets torch wrap a raw device allocation (no copy) through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int, owner):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+        self._owner = owner
+
+
+class PeerArena:
+    """One device allocation per rank that every rank of `group` (all on one node) maps into its own address
+    space (CUDA IPC).  The first `header_bytes` belong to the library's kernels; the rest is laid out by the
+    layer that owns the arena, identically on every rank.  Collective: every rank must construct it."""
+
+    def __init__(self, nbytes: int, group=None, device: torch.device | None = None):
+        from . import _lib
+        self._lib = lib = _lib.load()
+        self._check = _lib.check
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.header_bytes = lib.marlin_b200_peer_header_bytes()
+        self.nbytes = (int(nbytes) + 255) // 256 * 256
+        self._opened: list[int] = []
+        with torch.cuda.device(self.device):
+            base = ctypes.c_void_p()
+            self._check(lib.marlin_b200_peer_alloc(self.nbytes, ctypes.byref(base)))
+            self.base = base.value
+            handle = ctypes.create_string_buffer(64)
+            self._check(lib.marlin_b200_peer_export(self.base, handle))
+            handles = [None] * self.world
+            if self.world > 1:
+                dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            ptrs = []
+            for r in range(self.world):
+                if r == self.rank:
+                    ptrs.append(self.base)
+                    continue
+                peer = ctypes.c_void_p()
+                self._check(lib.marlin_b200_peer_open(ctypes.create_string_buffer(handles[r], 64), ctypes.byref(peer)))
+                self._opened.append(peer.value)
+                ptrs.append(peer.value)
+        self.table = (ctypes.c_void_p * self.world)(*ptrs)
+        self._bytes = torch.as_tensor(_DeviceBytes(self.base, self.nbytes, self), device=self.device)
+        if self.world > 1:
+            dist.barrier(group=group)
+
+    def tensor(self, offset: int, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """A tensor over the local arena at `offset` (a multiple of 256 behind the header)."""
+        if offset < self.header_bytes or offset % 256:
+            raise ValueError("arena offsets are multiples of 256 bytes behind the library's header")
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        if offset + nbytes > self.nbytes:
+            raise ValueError("tensor does not fit the arena")
+        return self._bytes[offset:offset + nbytes].view(dtype).view(shape)
+
+    def status(self) -> tuple[int, int]:
+        """(status, steps completed); 0 = no wait of this arena's kernels has given up.  Synchronous."""
+        st, ep = ctypes.c_int(0), ctypes.c_int(0)
+        with torch.cuda.device(self.device):
+            self._check(self._lib.marlin_b200_peer_status(self.base, ctypes.byref(st), ctypes.byref(ep)))
+        return int(st.value), int(ep.value)
+
+    def close(self):
+        """Collective: unmaps the peers' arenas and frees this rank's once every rank has stopped using them."""
+        if self.base is None:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            for ptr in self._opened:
+                self._lib.marlin_b200_peer_close(ptr)
+            self._opened = []
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            self._bytes = None
+            self._lib.marlin_b200_peer_free(self.base)
+            self.base = None
 
 
 # --------------------------------------------------------------------------------------------------
@@ -41,16 +137,42 @@ def column_slice(n: int, rank: int, world: int) -> tuple[int, int]:
 class ColumnParallelMarlinLinear:
     """y[M, N] = x[M, K] @ W[K, N] with W's columns sharded over the ranks of `group`."""
 
-    def __init__(self, gemm: Callable[[torch.Tensor, torch.Tensor], None], n_total: int, group=None):
-        """`gemm(x, out_slice)` runs this rank's local GEMM into `out_slice` [M, N/world]."""
+    def __init__(self, gemm: Callable[[torch.Tensor, torch.Tensor], None], n_total: int, group=None,
+                 use_peer_memory: bool = False, max_m: int = 16, dtype: torch.dtype = torch.bfloat16):
+        """`gemm(x, out_slice)` runs this rank's local GEMM into `out_slice` [M, N/world].
+        `use_peer_memory`: gather with the library's peer-store kernel (GPUs of one node, M <= max_m); the
+        buffers are allocated once, here, and the step has no host synchronisation (it can be captured)."""
         self.gemm, self.n_total, self.group = gemm, n_total, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.lo, self.hi = column_slice(n_total, self.rank, self.world)
+        self.arena = None
+        if use_peer_memory and self.world > 1:
+            per = self.hi - self.lo
+            self._slice_bytes = max_m * per * torch.empty((), dtype=dtype).element_size()
+            self.max_m, self.dtype = max_m, dtype
+            self.arena = PeerArena(4096 + 2 * self.world * self._slice_bytes, group)
+            self._local = torch.empty((max_m, per), dtype=dtype, device=self.arena.device)
+            self._out = torch.empty((max_m, n_total), dtype=dtype, device=self.arena.device)
+
+    def gather(self, local: torch.Tensor) -> torch.Tensor:
+        """Peer-memory all-gather of this rank's [M, N/world] block (contiguous, M <= max_m) into the layer's
+        [M, N] output buffer: one kernel, no host synchronisation."""
+        from . import _lib
+        m, per = local.shape
+        a, out = self.arena, self._out[:m]
+        _lib.check(a._lib.marlin_b200_peer_allgather(a.table, self.rank, self.world, local.data_ptr(),
+                                                     m * per * local.element_size(), 4096, out.data_ptr(), m,
+                                                     torch.cuda.current_stream(a.device).cuda_stream))
+        return out
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         m = x.shape[0]
         per = self.hi - self.lo
+        if self.arena is not None and m <= self.max_m and x.dtype == self.dtype:
+            local = self._local[:m]
+            self.gemm(x, local)
+            return self.gather(local)
         gathered = torch.empty((self.world, m, per), dtype=x.dtype, device=x.device)
         self.gemm(x, gathered[self.rank])
         if self.world > 1:
@@ -204,6 +326,101 @@ class ExpertParallelMoE:
         self.last_recv_rows = 0   # rows this rank's experts received in the last forward (load report)
         self.record_phases = False   # CUDA events between the phases of every forward, read by phase_ms()
         self._marks = []
+        self.arena = None
+
+    def enable_peer_memory(self, capacity_rows: int, hidden: int, dtype: torch.dtype, device=None):
+        """Collective.  Switches the layer to the library's peer-memory kernels (GPUs of one node): receive and
+        output buffers of `capacity_rows` rows are allocated once on every rank and mapped by all ranks.
+        `capacity_rows` bounds the routes one rank can receive in a step (tokens of all ranks * top_k is always
+        enough); a step that exceeds it raises."""
+        row_bytes = hidden * torch.empty((), dtype=dtype).element_size()
+        if row_bytes % 16:
+            raise ValueError("hidden size must give rows of a multiple of 16 bytes")
+        up = lambda v: (v + 255) // 256 * 256
+        off_rows = 4096
+        off_expert = up(off_rows + capacity_rows * row_bytes)
+        off_weight = up(off_expert + capacity_rows * 4)
+        off_out = up(off_weight + capacity_rows * 4)
+        self.arena = PeerArena(off_out + capacity_rows * row_bytes, self.group, device)
+        a = self.arena
+        self._layout = (ctypes.c_int64 * 6)(off_rows, off_expert, off_weight, off_out, capacity_rows, row_bytes)
+        self._recv_rows = a.tensor(off_rows, (capacity_rows, hidden), dtype)
+        self._recv_expert = a.tensor(off_expert, (capacity_rows,), torch.int32)
+        self._recv_weight = a.tensor(off_weight, (capacity_rows,), torch.float32)
+        self._out_rows = a.tensor(off_out, (capacity_rows, hidden), dtype)
+        host, dev = ctypes.c_void_p(), ctypes.c_void_p()
+        with torch.cuda.device(a.device):
+            a._check(a._lib.marlin_b200_peer_host_word_alloc(ctypes.byref(host), ctypes.byref(dev)))
+        self._host_word, self._host_word_dev = host.value, dev.value
+        self._step = 0
+        if self.expert_slot is None:
+            self.expert_slot = torch.arange(self.num_experts, dtype=torch.int32, device=a.device)
+        else:
+            self.expert_slot = self.expert_slot.to(a.device)
+
+    def close(self):
+        """Collective: releases the peer-memory buffers."""
+        if self.arena is not None:
+            self.arena.close()
+            self.arena._lib.marlin_b200_peer_host_word_free(self._host_word)
+            self.arena = None
+
+    def _forward_peer(self, hidden: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        from . import ops
+        a, lib = self.arena, self.arena._lib
+        t, h = hidden.shape
+        k = topk_ids.shape[1]
+        numel = t * k
+        dev = hidden.device
+        if not (hidden.is_contiguous() and topk_ids.is_contiguous() and topk_weights.is_contiguous()):
+            raise RuntimeError("the expert-parallel layer takes contiguous tensors")
+        if hidden.dtype != self._recv_rows.dtype or h != self._recv_rows.shape[1]:
+            raise RuntimeError("hidden does not match the shape / dtype the peer buffers were made for")
+        ids32 = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
+        w32 = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.to(torch.float32)
+        order = torch.empty(numel, dtype=torch.int32, device=dev)
+        slot_sorted = torch.empty(numel + 1, dtype=torch.int32, device=dev)
+        num_valid = torch.empty(1, dtype=torch.int32, device=dev)
+        position = torch.empty(numel, dtype=torch.int32, device=dev)
+        out = torch.empty_like(hidden)
+        ops.moe_align_block_size(ids32, self.num_experts, 1, order, slot_sorted, num_valid, self.expert_slot)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rank, world, per = self.rank, self.world, self.experts_per_rank
+        a._check(lib.marlin_b200_ep_plan(a.table, rank, world, slot_sorted.data_ptr(), numel, per, stream))
+        a._check(lib.marlin_b200_ep_dispatch(a.table, rank, world, self._layout, hidden.data_ptr(), order.data_ptr(),
+                                             slot_sorted.data_ptr(), w32.data_ptr(), position.data_ptr(), k, per,
+                                             self._host_word_dev, stream))
+        self._step += 1
+        rows, invalid, status = ctypes.c_int64(0), ctypes.c_int(0), ctypes.c_int(0)
+        # the row total arrives through mapped host memory while the dispatch kernel is still copying rows
+        a._check(lib.marlin_b200_ep_poll_rows(self._host_word, self._step, 10000, ctypes.byref(rows),
+                                              ctypes.byref(invalid), ctypes.byref(status)))
+        self._mark("plan")
+        if status.value:
+            raise RuntimeError(f"expert-parallel step {self._step}: peer-memory status {status.value} "
+                               "(1 + phase of a wait that gave up after two seconds, or 16 = receive capacity)")
+        if invalid.value:
+            # every rank sees the same count: all close the step and raise
+            a._check(lib.marlin_b200_ep_signal(a.table, rank, world, 3, stream))
+            a._check(lib.marlin_b200_ep_combine(a.table, rank, world, self._layout, position.data_ptr(), k, t,
+                                                out.data_ptr(), ops._act_code(hidden.dtype), 1, stream))
+            raise RuntimeError("expert-parallel dispatch: topk_ids holds expert ids outside [0, num_experts)")
+        r = int(rows.value)
+        self.last_recv_rows = r
+        a._check(lib.marlin_b200_ep_wait(a.table, rank, world, 2, stream))
+        self._mark("dispatch")
+        if r > 0:
+            out_rows = self._out_rows[:r]
+            if getattr(self.compute, "takes_out", False):
+                self.compute(self._recv_rows[:r], self._recv_expert[:r], self._recv_weight[:r], out=out_rows)
+            else:
+                out_rows.copy_(self.compute(self._recv_rows[:r], self._recv_expert[:r], self._recv_weight[:r]))
+        self._mark("experts")
+        a._check(lib.marlin_b200_ep_signal(a.table, rank, world, 3, stream))
+        a._check(lib.marlin_b200_ep_combine(a.table, rank, world, self._layout, position.data_ptr(), k, t,
+                                            out.data_ptr(), ops._act_code(hidden.dtype), 0, stream))
+        self._mark("combine")
+        return out
 
     @classmethod
     def from_marlin_weights(cls, w13, w2, w13_scale, w2_scale, quant_type_id: int, num_experts: int, group=None,
@@ -212,13 +429,15 @@ class ExpertParallelMoE:
         """w13 / w2: this rank's experts ([E/world, ...], in slot order) in the packed layout of the grouped GEMM."""
         from . import fused_moe
 
-        def compute(rows, local_expert, weights):
+        def compute(rows, local_expert, weights, out=None):
             if rows.shape[0] == 0:
                 return rows.new_empty(rows.shape)
             return fused_moe.fused_marlin_moe(rows, w13, w2, None, None, w13_scale, w2_scale,
                                               weights.reshape(-1, 1).contiguous(), local_expert.reshape(-1, 1).contiguous(),
                                               quant_type_id, global_scale1=global_scale1, global_scale2=global_scale2,
-                                              w1_zeros=w13_zeros, w2_zeros=w2_zeros)
+                                              w1_zeros=w13_zeros, w2_zeros=w2_zeros, output=out)
+
+        compute.takes_out = True
 
         if expert_slot is not None:
             expert_slot = expert_slot.to(w13.device)
@@ -243,6 +462,8 @@ class ExpertParallelMoE:
         """hidden [T, H] (this rank's tokens), topk_* [T, k] with GLOBAL expert ids -> [T, H]."""
         self._marks = []
         self._mark("start")
+        if self.arena is not None:
+            return self._forward_peer(hidden, topk_weights, topk_ids)
         t, h = hidden.shape
         k = topk_ids.shape[1]
         slot = self.expert_slot

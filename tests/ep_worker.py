@@ -47,10 +47,36 @@ def main():
     ok = torch.equal(ids.cpu(), rids[sl_t]) and mo.within_tolerance(out.cpu(), ref)
     # the placement must spread the routes: no rank receives more than 1.5x its even share
     ok = ok and layer.last_recv_rows <= 1.5 * tokens * k / world
+    why = "" if ok else "collective transport; "
+
+    # the same layer over peer-mapped memory: same bits, step after step
+    layer.enable_peer_memory(tokens * k, hdim, dtype)
+    for step in range(3):
+        out_peer = layer.forward(hidden[sl_t].to(dev), tw, ids)
+        torch.cuda.synchronize()
+        if not torch.equal(out_peer, out):
+            ok, why = False, why + f"peer transport differs at step {step}; "
+    # an expert id outside the table on ONE rank: every rank raises, and the next step still works
+    bad = ids.clone()
+    if rank == world - 1:
+        bad[0, 0] = e
+    try:
+        layer.forward(hidden[sl_t].to(dev), tw, bad)
+        ok, why = False, why + "invalid id not reported; "
+    except RuntimeError as err:
+        if "outside" not in str(err):
+            ok, why = False, why + f"unexpected error {err}; "
+    out_peer = layer.forward(hidden[sl_t].to(dev), tw, ids)
+    torch.cuda.synchronize()
+    if not torch.equal(out_peer, out) or layer.arena.status()[0] != 0:
+        ok, why = False, why + "step after the refused one differs; "
+    layer.close()
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
         print("EP_OK" if int(flag) == 1 else f"EP_FAIL mean_rel={mo.mean_rel_err(out.cpu(), ref):.3e}", flush=True)
+    if why:
+        print(f"rank {rank}: {why}", flush=True)
     dist.destroy_process_group()
     sys.exit(0 if int(flag) == 1 else 1)
 
