@@ -302,7 +302,7 @@ int marlin_b200_peer_host_word_free(void* host_ptr);
 /* Column-parallel dense layer: every rank's `src` (bytes_per_rank bytes, a multiple of 16) gathered into
  * `out`.  slice_rows == 0: out is [world][bytes_per_rank].  slice_rows == M: src is an [M, cols] row block and
  * out is [M, world * cols] (rank r's columns at r * cols).  The arena holds two gather buffers of
- * world * bytes_per_rank bytes at buffer_offset.  No host synchronisation: the call can be captured. */
+ * 2 * world * bytes_per_rank bytes at buffer_offset (every 8 data bytes travel with 8 bytes of step number).  No host synchronisation: the call can be captured. */
 int marlin_b200_peer_allgather(const void* const* arenas, int rank, int world, const void* src,
                                int64_t bytes_per_rank, int64_t buffer_offset, void* out, int64_t slice_rows,
                                void* stream);

@@ -4,7 +4,8 @@
 // library kernel ever touches a peer address.
 //
 //  * peer_allgather_kernel: the column-parallel dense layer.  Every rank stores its [M, N/world] slice into
-//    every rank's gather buffer, signals, waits for all slices and copies the assembled rows out.
+//    every rank's gather buffer with the step number inside every stored unit, polls the units the other
+//    ranks store into its own buffer and writes the assembled rows out.
 //  * the expert-parallel layer, one step:
 //      ep_plan_kernel      rows per destination rank from the sorted route list; the counts go to every
 //                          rank's count table (signal A)
@@ -132,8 +133,21 @@ __device__ void finish_step(PeerHeader* me, unsigned int epoch, unsigned int* do
 // ---------------------------------------------------------------------------------------------------------
 // dense column-parallel layer: all-gather of [M, N/world] slices
 // ---------------------------------------------------------------------------------------------------------
-// gather buffers: arena + buf_off, [2 (epoch parity)][world][vecs] of 16 bytes
-__global__ void __launch_bounds__(512) peer_allgather_kernel(PeerTable tab, int rank, int world,
+// The slices are small (decode sizes), so the step is bound by latency, not by bytes: data and flag travel in
+// the same store (every 16-byte unit is {4 data bytes, epoch, 4 data bytes, epoch}, each 8-byte half atomic on
+// its own), the receiver polls the units themselves, and no fence, separate flag or arrival counter sits on
+// the path.  Every thread issues all its stores before it polls, so no CTA waits for another CTA of its own
+// grid.  gather buffers: arena + buf_off, [2 (epoch parity)][world][2 * vecs] of 16 bytes.
+__device__ __forceinline__ uint4 ld_volatile(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256) peer_allgather_kernel(PeerTable tab, int rank, int world,
                                                              const uint4* __restrict__ src, int64_t vecs,
                                                              int64_t buf_off, uint4* __restrict__ out,
                                                              int64_t slice_rows) {
@@ -142,25 +156,46 @@ __global__ void __launch_bounds__(512) peer_allgather_kernel(PeerTable tab, int 
   const int64_t par = epoch & 1;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // slice_rows > 0: the slices are [slice_rows, cols] row blocks and out is [slice_rows, world * cols]
+  const int64_t row_vecs = slice_rows > 0 ? vecs / slice_rows : vecs;
+  auto out_index = [&](int64_t r, int64_t v) {
+    return slice_rows > 0 ? ((v / row_vecs) * world + r) * row_vecs + v % row_vecs : r * vecs + v;
+  };
   for (int64_t idx = first; idx < vecs * world; idx += stride) {
     const int p = (int)(idx / vecs);
     const int64_t v = idx % vecs;
-    uint4* dst = reinterpret_cast<uint4*>(tab.base[p] + buf_off) + (par * world + rank) * vecs + v;
-    *dst = src[v];
-  }
-  signal_phase(tab, rank, world, kGather, epoch, &me->done[0]);
-  if (wait_phase(me, world, kGather, epoch)) {
-    const uint4* buf = reinterpret_cast<const uint4*>(tab.base[rank] + buf_off) + par * world * vecs;
-    // slice_rows > 0: the slices are [slice_rows, cols] row blocks and out is [slice_rows, world * cols]
-    const int64_t row_vecs = slice_rows > 0 ? vecs / slice_rows : vecs;
-    for (int64_t idx = first; idx < vecs * world; idx += stride) {
-      int64_t o = idx;
-      if (slice_rows > 0) {
-        const int64_t r = idx / vecs, w = idx % vecs;
-        o = ((w / row_vecs) * world + r) * row_vecs + w % row_vecs;
-      }
-      out[o] = ld_cg(buf + idx);
+    const uint4 x = src[v];
+    if (p == rank) {
+      out[out_index(rank, v)] = x;
+    } else {
+      uint4* dst = reinterpret_cast<uint4*>(tab.base[p] + buf_off) + ((par * world + rank) * vecs + v) * 2;
+      dst[0] = make_uint4(x.x, epoch, x.y, epoch);
+      dst[1] = make_uint4(x.z, epoch, x.w, epoch);
     }
+  }
+  bool gave_up = (*(volatile unsigned int*)&me->status != 0u);
+  const uint4* buf = reinterpret_cast<const uint4*>(tab.base[rank] + buf_off) + par * world * vecs * 2;
+  for (int64_t idx = first; idx < vecs * world && !gave_up; idx += stride) {
+    const int r = (int)(idx / vecs);
+    const int64_t v = idx % vecs;
+    if (r == rank) continue;
+    const uint4* slot = buf + idx * 2;
+    uint4 a = ld_volatile(slot), b = ld_volatile(slot + 1);
+    unsigned long long t0 = 0;
+    for (unsigned int spin = 0; a.y != epoch || a.w != epoch || b.y != epoch || b.w != epoch; ++spin) {
+      if ((spin & 255u) == 255u) {
+        const unsigned long long now = global_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > WAIT_NS) {
+          atomicCAS(&me->status, 0u, 1u + (unsigned)kGather);
+          gave_up = true;
+          break;
+        }
+      }
+      a = ld_volatile(slot);
+      b = ld_volatile(slot + 1);
+    }
+    if (!gave_up) out[out_index(r, v)] = make_uint4(a.x, a.z, b.x, b.z);
   }
   finish_step(me, epoch, &me->done[1]);
 }
@@ -439,10 +474,9 @@ extern "C" int marlin_b200_peer_allgather(const void* const* arenas, int rank, i
   MB_CHECK(slice_rows >= 0 && (slice_rows == 0 || vecs % slice_rows == 0),
            "a slice of %lld bytes does not split into %lld rows of whole 16-byte units", (long long)bytes_per_rank,
            (long long)slice_rows);
-  const int64_t want = (vecs * world + 511) / 512;
-  // every CTA waits for the other ranks, so all CTAs of the grid must be resident at once: at most one per SM
-  const int grid = (int)(want < sm_count() ? (want > 0 ? want : 1) : sm_count());
-  peer_allgather_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(tab, rank, world, (const uint4*)src, vecs,
+  const int64_t want = (vecs * world + 255) / 256, cap = (int64_t)sm_count() * 4;
+  const int grid = (int)(want < cap ? (want > 0 ? want : 1) : cap);
+  peer_allgather_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(tab, rank, world, (const uint4*)src, vecs,
                                                                 buffer_offset, (uint4*)out, slice_rows);
   MB_CUDA(cudaGetLastError());
   count_launches(1);

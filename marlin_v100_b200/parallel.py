@@ -151,7 +151,7 @@ class ColumnParallelMarlinLinear:
             per = self.hi - self.lo
             self._slice_bytes = max_m * per * torch.empty((), dtype=dtype).element_size()
             self.max_m, self.dtype = max_m, dtype
-            self.arena = PeerArena(4096 + 2 * self.world * self._slice_bytes, group)
+            self.arena = PeerArena(4096 + 4 * self.world * self._slice_bytes, group)
             self._local = torch.empty((max_m, per), dtype=dtype, device=self.arena.device)
             self._out = torch.empty((max_m, n_total), dtype=dtype, device=self.arena.device)
 
