@@ -35,8 +35,9 @@
 // producer | 17 and 19 MMA issuers (one 128-column tile each, on two different SM partitions: issuing is what
 // an MMA of this size costs; 17 owns the tensor memory) | 18 producer of the small per-chunk operands (digit
 // tile, digit sums, scale and zero rows) | 20-23 cross-CTA sums of the column groups shared with other CTAs.
-// Four accumulator buffers and four operand stages in tensor memory: the round trip MMA -> epilogue -> next MMA
-// on the same buffer (about 1500 cycles) bounds the rate at one chunk per round trip / buffers.
+// Four operand stages and four (up to 16 rows) or eight (up to 8 rows) accumulator buffers in tensor memory: the
+// round trip MMA -> epilogue -> next MMA on the same buffer (about 1500 cycles) bounds the rate at one chunk per
+// round trip / buffers.
 // A stage's 16 KiB of packed weights are released as soon as the dequant warps have read them and refilled at
 // once, so all eight stages cover the DRAM latency; the small operands (7 KiB, served by L2) stay until the
 // chunk's MMAs and epilogue are done.
