@@ -19,8 +19,6 @@
 //   B ring     : dequant warps -> MMA                (b_full / b_empty via tcgen05.commit)
 //   accumulator: MMA -> epilogue -> MMA              (acc_full via tcgen05.commit / acc_empty)
 //
-// Compiling with -DMB_TC_PROFILE adds per-role wait-cycle counters for CTA 0 and a debug entry point
-// that reads them; release builds carry neither.
 
 #include <cstdint>
 #include "codes.cuh"
@@ -135,15 +133,6 @@ struct TcWalk {
   }
 };
 
-#ifdef MB_TC_PROFILE
-// Per-role wait-cycle counters of CTA 0 (debug builds only): [role][slot]
-__device__ unsigned long long g_tc_prof[8][4];
-#define PROF_T0() const long long prof_t0__ = clock64()
-#define PROF_ADD(role, slot) if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_tc_prof[role][slot], (unsigned long long)(clock64() - prof_t0__))
-#else
-#define PROF_T0()
-#define PROF_ADD(role, slot)
-#endif
 
 // kind::f16 instruction descriptor: fp32 accumulate, A and B both T, both K-major, M = 128, N = 256.
 template <typename T>
@@ -804,9 +793,7 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       bool ok = true;
       while (ok && iter.next(e, row_lo, row_hi)) {
         for (int c = 0; c < p.kc; ++c) {
-          { PROF_T0();
           if (!mbar_wait(raw_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 11); ok = false; break; }
-          PROF_ADD(0, 0); }
           const uint32_t st = base + L::OFF_RAW + s * L::RAW_BYTES;
           mbar_arrive_expect_tx(raw_full(s), p.raw_tx);
           // experts are stacked along the k-tile rows (weights) and along the group rows (scales)
@@ -832,9 +819,7 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       while (ok && iter.next(e, row_lo, row_hi)) {
         const int row0 = iter.row0();
         for (int c = 0; c < p.kc; ++c) {
-          { PROF_T0();
           if (!mbar_wait(a_empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 12); ok = false; break; }
-          PROF_ADD(1, 0); }
           mbar_arrive_expect_tx(a_full(s), L::A_BYTES);
           tma_load_2d(base + L::OFF_A + s * L::A_BYTES, &tmA, a_full(s), c * BK, row0);
           if (++s == AS) { s = 0; ph ^= 1u; }
@@ -852,12 +837,8 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (!mbar_wait(acc_empty, phacc ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 13); ok = false; break; }
         tc_fence_after();
         for (int c = 0; c < p.kc; ++c) {
-          { PROF_T0();
           if (!mbar_wait(a_full(sa), pha, &s_abort)) { atomicExch(&g_tc_status, 14); ok = false; break; }
-          PROF_ADD(2, 0); }
-          { PROF_T0();
           if (!mbar_wait(b_full(sb), phb, &s_abort)) { atomicExch(&g_tc_status, 14); ok = false; break; }
-          PROF_ADD(2, 1); }
           tc_fence_after();
           const uint32_t a_addr = base + L::OFF_A + sa * L::A_BYTES;
           const uint32_t b_addr = base + L::OFF_B + sb * L::B_BYTES;
@@ -938,19 +919,12 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     bool ok = true;
     while (ok && iter.next(e, row_lo, row_hi)) {
       for (int c = 0; c < p.kc; ++c) {
-        { PROF_T0();
         if (!mbar_wait(raw_full(sr), phr, &s_abort)) { atomicExch(&g_tc_status, 16); ok = false; break; }
-        if (d == 0) PROF_ADD(3, 0); }
-        { PROF_T0();
         if (!mbar_wait(b_empty(sb), phb ^ 1u, &s_abort)) { atomicExch(&g_tc_status, 16); ok = false; break; }
-        if (d == 0) PROF_ADD(3, 1); }
-        PROF_T0();
         dequant_chunk<T, FMT>(base + L::OFF_RAW + sr * L::RAW_BYTES, base + L::OFF_B + sb * L::B_BYTES, d, lane,
                               p.rpc, p.group_size);
-        if (d == 0) PROF_ADD(3, 2);
         fence_proxy_async();
         __syncwarp();
-        if (d == 0) PROF_ADD(3, 3);
         if (lane == 0) {
           mbar_arrive(b_full(sb));
           mbar_arrive(raw_empty(sr));
@@ -1292,14 +1266,3 @@ int read_tc_status(int* value, bool reset) {
 
 
 }  // namespace mb200
-
-#ifdef MB_TC_PROFILE
-extern "C" int marlin_b200_debug_tc_prof(unsigned long long* out32, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(out32, mb200::g_tc_prof, sizeof(unsigned long long) * 32);
-  if (reset) {
-    unsigned long long z[32] = {};
-    cudaMemcpyToSymbol(mb200::g_tc_prof, z, sizeof(z));
-  }
-  return (int)e;
-}
-#endif
