@@ -166,10 +166,14 @@ __host__ __device__ inline int digit_pos(int k_local) {
 }
 
 // ---- activations -> digit planes -----------------------------------------------------------------------
-// One block per token row (8 or 16 blocks).  digits: int8 [2 * rows][K], row d * rows + m; rows of absent tokens
-// are zero.
+// digits: int8 [2 * rows][K], row d * rows + m; rows of absent tokens are zero.
+// 128 threads at no more than 32 registers: such a block fits into what a resident CTA of the GEMM kernel leaves
+// of an SM's register file (24 warps x 80 registers), so the blocks of the next call can sit beside the running
+// GEMM and the GEMM of this call can start beside them.
+constexpr int AD_THREADS = 128;
+
 template <typename T>
-__global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a, int64_t a_stride, int M, int K,
+__global__ void __launch_bounds__(AD_THREADS, 16) act_digits_kernel(const T* __restrict__ a, int64_t a_stride, int M, int K,
                                                          int8_t* __restrict__ digits, float* __restrict__ row_scale,
                                                          float* __restrict__ chunk_sums, int* __restrict__ counters,
                                                          int num_counters) {
@@ -177,24 +181,29 @@ __global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a
   // converts its own part of the row, so that the conversion of a row is spread over several SMs
   const int m = blockIdx.x, tid = threadIdx.x, ntok = gridDim.x;
   const int part = blockIdx.y, parts = gridDim.y;
+  // Launched with programmatic stream serialisation: the blocks may become resident while the kernel in front
+  // (the GEMM of the previous call, or any producer of the activations) still runs, so nothing in global memory
+  // is read or written before that kernel has completed; the GEMM behind may be scheduled at once (its weight
+  // stream does not depend on this kernel, its digit loads wait for this kernel's completion).
   pdl_release_dependents();
+  pdl_wait_prior_grid();
   if (m == 0 && part == 0)
-    for (int i = tid; i < num_counters; i += 256) counters[i] = 0;
-  __shared__ float s_red[8];
+    for (int i = tid; i < num_counters; i += AD_THREADS) counters[i] = 0;
+  __shared__ float s_red[AD_THREADS / 32];
   __shared__ float s_max;
   const int vecs = K / 8;
   const int v_begin = part * (vecs / parts), v_end = v_begin + vecs / parts;   // a multiple of 16 vectors (one chunk)
   if (m >= M) {
-    for (int v = v_begin + tid; v < v_end; v += 256)
+    for (int v = v_begin + tid; v < v_end; v += AD_THREADS)
 #pragma unroll
       for (int d = 0; d < NDIG; ++d) *reinterpret_cast<uint2*>(digits + (int64_t)(d * ntok + m) * K + v * 8) = make_uint2(0, 0);
-    for (int c = v_begin / 16 + tid; c < v_end / 16; c += 256) chunk_sums[c * ntok + m] = 0.f;
+    for (int c = v_begin / 16 + tid; c < v_end / 16; c += AD_THREADS) chunk_sums[c * ntok + m] = 0.f;
     if (tid == 0 && part == 0) row_scale[m] = 0.f;
     return;
   }
   const T* row = a + (int64_t)m * a_stride;
   float mx = 0.f;
-  for (int v = tid; v < vecs; v += 256) {
+  for (int v = tid; v < vecs; v += AD_THREADS) {
     const uint4 q = *reinterpret_cast<const uint4*>(row + v * 8);
     const T* e = reinterpret_cast<const T*>(&q);
 #pragma unroll
@@ -206,7 +215,7 @@ __global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a
   __syncthreads();
   if (tid == 0) {
     float t = s_red[0];
-    for (int i = 1; i < 8; ++i) t = fmaxf(t, s_red[i]);
+    for (int i = 1; i < AD_THREADS / 32; ++i) t = fmaxf(t, s_red[i]);
     s_max = t;
   }
   __syncthreads();
@@ -220,8 +229,8 @@ __global__ void __launch_bounds__(256) act_digits_kernel(const T* __restrict__ a
   // x = a * 2^(7 - e), |x| < 127.5; two exact power-of-two multiplies keep the factors in range
   const float f1 = ldexpf(1.f, (7 - e) / 2), f2 = ldexpf(1.f, (7 - e) - (7 - e) / 2);
   if (tid == 0 && part == 0) row_scale[m] = finite ? ldexpf(1.f, e - 7) : 0.f;
-  // K / 8 vectors, 16 per chunk; the 256 threads of a pass cover 16 whole chunks
-  for (int v0 = v_begin; v0 < v_end; v0 += 256) {
+  // K / 8 vectors, 16 per chunk; the threads of a pass cover 8 whole chunks
+  for (int v0 = v_begin; v0 < v_end; v0 += AD_THREADS) {
     const int v = v0 + tid;
     float sum = 0.f;
     if (v < v_end) {
@@ -310,20 +319,24 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       s_run_len[r] = rl[r];
     }
     s_abort = 0;
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full(s), 1);
-      mbar_init(fullm(s), 1);
-      mbar_init(empty(s), EPI_WARPS);
-      mbar_init(mma_done(s), 2);
-      mbar_init(raw_free(s), DQ_WARPS);
-    }
-    for (int t = 0; t < TSTAGES; ++t) mbar_init(a_ready(t), DQ_WARPS);
-    for (int r = 0; r < 2; ++r) mbar_init(part_ready(r), EPI_WARPS);
-    for (int b = 0; b < DBUFS; ++b) mbar_init(d_free(b), EPI_WARPS);
-    fence_barrier_init();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmS);
     if constexpr (format_has_zp(FMT)) prefetch_tensormap(&tmZ);
+  }
+  if (warp == 1) {
+    // barriers in the order of the accessors above; every lane initialises its share
+    for (int i = lane; i < NUM_BARS; i += 32) {
+      int count;
+      if (i < STAGES) count = 1;                                        // full
+      else if (i < 2 * STAGES) count = EPI_WARPS;                       // empty
+      else if (i < 3 * STAGES) count = 2;                               // mma_done
+      else if (i < 3 * STAGES + TSTAGES) count = DQ_WARPS;              // a_ready
+      else if (i < 4 * STAGES + TSTAGES) count = DQ_WARPS;              // raw_free
+      else if (i < 5 * STAGES + TSTAGES) count = 1;                     // fullm
+      else count = EPI_WARPS;                                           // part_ready, d_free
+      mbar_init(bar0 + 8u * i, count);
+    }
+    fence_barrier_init();
   }
   if (warp == MMA_WARP) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -669,12 +682,22 @@ int launch_one(const GemmArgs& g) {
   p.num_ctas = (int)(U < sm_count() ? U : sm_count());
   p.tx_bytes = C::ACT_BYTES + NTOK * 4 + kGroupN * 2 * (format_has_zp(FMT) ? 2 : 1);   // small operands of a chunk
 
-  int parts = 1;   // as many parts per row as leave every part whole chunks and at least one pass of 256 vectors
-  while (parts < 8 && K % (KCH * parts * 2) == 0 && K / (parts * 2) >= 2048) parts *= 2;
-  act_digits_kernel<T><<<dim3(NTOK, parts), 256, 0, g.stream>>>(reinterpret_cast<const T*>(g.a), g.a_stride, m, (int)K, digits,
-                                                 row_scale, chunk_sums, p.counters, p.ng);
-  MB_CUDA(cudaGetLastError());
-  count_launches(1);
+  int parts = 1;   // as many parts per row as leave every part whole chunks and at least one pass of the block
+  while (parts < 8 && K % (KCH * parts * 2) == 0 && K / (parts * 2) >= 8 * AD_THREADS) parts *= 2;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(NTOK, parts);
+    cfg.blockDim = dim3(AD_THREADS);
+    cfg.stream = g.stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MB_CUDA(cudaLaunchKernelEx(&cfg, act_digits_kernel<T>, reinterpret_cast<const T*>(g.a), g.a_stride, m, (int)K, digits,
+                               row_scale, chunk_sums, p.counters, p.ng));
+    count_launches(1);
+  }
   CUtensorMap tmA, tmS, tmZ;
   {
     const uint64_t dims[2] = {(uint64_t)N, (uint64_t)g.num_groups};
@@ -705,9 +728,6 @@ int launch_one(const GemmArgs& g) {
     MB_CUDA(cudaFuncSetAttribute(stream_i8_kernel<T, FMT, TOKH>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     attr_set[dev] = true;
   }
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.num_ctas);
   cfg.blockDim = dim3(C::THREADS);
