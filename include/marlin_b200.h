@@ -276,6 +276,31 @@ int marlin_b200_moe_sum_rows(const void* in, const int32_t* rows, void* out, int
                              int64_t hidden, int act_dtype, void* stream);
 
 /* ----------------------------------------------------------------------------------------------
+ * Load-time helpers for expert layers and fp4 / fp8 checkpoints.
+ * gptq_moe_repack / awq_moe_repack: all experts of a layer in one launch (b_q_weight [E][...], perm [E][size_k]
+ *   or NULL, out [E][size_k / 16][size_n * 16 / pack_factor]); stand in for the per-expert Python loops
+ *   gptq_marlin_moe_repack / awq_marlin_moe_repack   vllm/_custom_ops.py:1228-1269
+ * nvfp4_scale_min + nvfp4_process_scales: block scales (fp16 values of the e4m3 scales, [rows][cols]) -> the
+ *   interleaved S0E5M3 bytes; scale_min leaves min(scale * 2^7 over non-zero scales) in *min_out (a device float)
+ *   from which the caller derives the power-of-two rescale (2^ceil(log2(2 / min)) if min < 2, bf16 activations only)
+ *   nvfp4_marlin_process_scales   .../quantization/utils/marlin_utils_fp4.py:30-112
+ * interleave_scale_bytes: the [0,2,1,3] interleave per four columns of one-byte (e8m0) scales
+ *   mxfp4_marlin_process_scales   .../marlin_utils_fp4.py:115-129 (marlin_b200_gemm itself takes mxfp4 scales in
+ *   natural column order: this is for callers that hold the reference's own form)
+ * fp8_fuse_exponent_bias: scales * 2^8 (fp16) / 2^120 (bf16)
+ *   fp8_fused_exponent_bias_into_scales   .../marlin_utils_fp8.py:28-39
+ * -------------------------------------------------------------------------------------------- */
+int marlin_b200_gptq_moe_repack(const int32_t* b_q_weight, const int32_t* perm, int32_t* out, int64_t num_experts,
+                                int64_t size_k, int64_t size_n, int num_bits, void* stream);
+int marlin_b200_awq_moe_repack(const int32_t* b_q_weight, int32_t* out, int64_t num_experts, int64_t size_k,
+                               int64_t size_n, int num_bits, void* stream);
+int marlin_b200_nvfp4_scale_min(const void* scales_half, int64_t count, float* min_out, void* stream);
+int marlin_b200_nvfp4_process_scales(const void* scales_half, uint8_t* out, int64_t rows, int64_t cols,
+                                     float scale_factor, void* stream);
+int marlin_b200_interleave_scale_bytes(const uint8_t* in, uint8_t* out, int64_t rows, int64_t cols, void* stream);
+int marlin_b200_fp8_fuse_exponent_bias(const void* in, void* out, int64_t count, int act_dtype, void* stream);
+
+/* ----------------------------------------------------------------------------------------------
  * Multi-GPU steps over peer-mapped memory.  No counterpart in the reference, whose distributed layer is a
  * world-size-1 stub (vllm/distributed/__init__.py:4-25); the layouts stand on its `expert_map` hook
  * (fused_marlin_moe.py:170-171) and on output columns being independent (marlin.cu:356-359).

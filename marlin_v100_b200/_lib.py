@@ -43,6 +43,12 @@ SIGNATURES = {
     "marlin_b200_silu_and_mul": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
     "marlin_b200_moe_sum": (_int, [_vp, _vp, _i64, _int, _i64, _int, _vp]),
     "marlin_b200_moe_sum_rows": (_int, [_vp, _vp, _vp, _i64, _int, _i64, _int, _vp]),
+    "marlin_b200_gptq_moe_repack": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "marlin_b200_awq_moe_repack": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "marlin_b200_nvfp4_scale_min": (_int, [_vp, _i64, _vp, _vp]),
+    "marlin_b200_nvfp4_process_scales": (_int, [_vp, _vp, _i64, _i64, _c.c_float, _vp]),
+    "marlin_b200_interleave_scale_bytes": (_int, [_vp, _vp, _i64, _i64, _vp]),
+    "marlin_b200_fp8_fuse_exponent_bias": (_int, [_vp, _vp, _i64, _int, _vp]),
     "marlin_b200_peer_header_bytes": (_int, []),
     "marlin_b200_peer_alloc": (_int, [_i64, _vp]),
     "marlin_b200_peer_free": (_int, [_vp]),

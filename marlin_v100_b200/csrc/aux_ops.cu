@@ -4,6 +4,10 @@
 //    (symmetric checkpoints) or the code's own AWQ zero-point
 //    (csrc/quantization/marlin/marlin_int4_fp8_preprocess.cu:8-56 of the reference).  One thread per packed
 //    word of eight codes, any tensor shape.
+//  * scale re-encoders of the fp4 / fp8 checkpoints, which the reference runs as eager PyTorch at load time
+//    (vllm/model_executor/layers/quantization/utils/marlin_utils_fp4.py:30-129, marlin_utils_fp8.py:28-39):
+//    nvfp4 block scales -> the S0E5M3 bytes the GEMM reads (with the power-of-two rescale and its minimum
+//    search), the [0,2,1,3] byte interleave of mxfp4 scales, fp8 scales times 2^bias.
 //  * marlin_b200_batched_moe_align_block_size: block lists for tokens that are already grouped by expert
 //    (csrc/moe/moe_align_sum_kernels.cu:22-78,571-596).  Every output position finds its expert by a
 //    search in the prefix sums, so the kernel is one pass over the outputs on any number of CTAs.
@@ -99,10 +103,121 @@ __global__ void __launch_bounds__(256) batched_align_kernel(const int32_t* __res
   }
 }
 
+// smallest non-zero value of h * 2^7 over all scales, as float bits (positive floats order like unsigned ints)
+__global__ void __launch_bounds__(256) nvfp4_scale_min_kernel(const __half* __restrict__ in, int64_t count,
+                                                              unsigned int* __restrict__ min_bits) {
+  unsigned int best = 0x7f800000u;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = __half2float(in[i]) * 128.f;
+    if (v > 0.f) best = min(best, __float_as_uint(v));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+  if ((threadIdx.x & 31) == 0 && best != 0x7f800000u) atomicMin(min_bits, best);
+}
+
+// out[r][4 q + j] = encode(in[r][4 q + {0,2,1,3}[j]]): times scale_factor (rounded to half), times 2^7 in half,
+// the half's bits shifted left by one, high byte
+__global__ void __launch_bounds__(256) nvfp4_process_scales_kernel(const __half* __restrict__ in,
+                                                                   uint8_t* __restrict__ out, int64_t count,
+                                                                   float scale_factor) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
+    const int j = (int)(i & 3);
+    const int64_t src = (i & ~(int64_t)3) + ((j == 1) ? 2 : (j == 2) ? 1 : j);
+    __half h = in[src];
+    if (scale_factor > 1.f) h = __float2half_rn(__half2float(h) * scale_factor);
+    h = __hmul(h, __float2half_rn(128.f));
+    const unsigned short bits = (unsigned short)(__half_as_ushort(h) << 1);
+    out[i] = (uint8_t)(bits >> 8);
+  }
+}
+
+__global__ void __launch_bounds__(256) interleave_bytes4_kernel(const uint8_t* __restrict__ in,
+                                                                uint8_t* __restrict__ out, int64_t count) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
+    const int j = (int)(i & 3);
+    out[i] = in[(i & ~(int64_t)3) + ((j == 1) ? 2 : (j == 2) ? 1 : j)];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) fp8_fuse_bias_kernel(const T* __restrict__ in, T* __restrict__ out,
+                                                            int64_t count, float factor) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = from_float<T>(to_float<T>(in[i]) * factor);
+}
+
+int elementwise_grid(int64_t count) {
+  const int64_t want = (count + 255) / 256, cap = (int64_t)sm_count() * 16;
+  return (int)(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
 }  // namespace
 }  // namespace mb200
 
 using namespace mb200;
+
+// Smallest non-zero scale times 2^7 of an nvfp4 scale tensor (fp16), written to *min_out as a float (+inf when
+// every scale is zero).  The caller derives the rescale: 2^ceil(log2(2 / min)) when min < 2, else 1.
+extern "C" int marlin_b200_nvfp4_scale_min(const void* scales_half, int64_t count, float* min_out, void* stream) {
+  MB_CHECK(count >= 0 && min_out != nullptr, "bad arguments");
+  auto s = (cudaStream_t)stream;
+  const unsigned int inf_bits = 0x7f800000u;
+  MB_CUDA(cudaMemcpyAsync(min_out, &inf_bits, sizeof(inf_bits), cudaMemcpyHostToDevice, s));
+  if (count == 0) return 0;
+  MB_CHECK(scales_half != nullptr, "null tensor pointer");
+  nvfp4_scale_min_kernel<<<elementwise_grid(count), 256, 0, s>>>((const __half*)scales_half, count,
+                                                                 reinterpret_cast<unsigned int*>(min_out));
+  MB_CUDA(cudaGetLastError());
+  count_launches(1);
+  return 0;
+}
+
+// nvfp4 block scales (fp16 values of the e4m3 scales, [rows][cols], cols % 4 == 0) -> the bytes the GEMM reads.
+extern "C" int marlin_b200_nvfp4_process_scales(const void* scales_half, uint8_t* out, int64_t rows, int64_t cols,
+                                                float scale_factor, void* stream) {
+  MB_CHECK(rows >= 0 && cols >= 0 && cols % 4 == 0, "scale columns must be a multiple of 4");
+  MB_CHECK(scale_factor >= 1.f, "scale_factor must be a power of two >= 1");
+  const int64_t count = rows * cols;
+  if (count == 0) return 0;
+  MB_CHECK(scales_half != nullptr && out != nullptr, "null tensor pointer");
+  nvfp4_process_scales_kernel<<<elementwise_grid(count), 256, 0, (cudaStream_t)stream>>>(
+      (const __half*)scales_half, out, count, scale_factor);
+  MB_CUDA(cudaGetLastError());
+  count_launches(1);
+  return 0;
+}
+
+// The [0,2,1,3] interleave per four columns of one-byte scales (mxfp4's e8m0 bytes in the reference's own form).
+extern "C" int marlin_b200_interleave_scale_bytes(const uint8_t* in, uint8_t* out, int64_t rows, int64_t cols,
+                                                  void* stream) {
+  MB_CHECK(rows >= 0 && cols >= 0 && cols % 4 == 0, "scale columns must be a multiple of 4");
+  const int64_t count = rows * cols;
+  if (count == 0) return 0;
+  MB_CHECK(in != nullptr && out != nullptr && in != out, "null or aliased tensor pointer");
+  interleave_bytes4_kernel<<<elementwise_grid(count), 256, 0, (cudaStream_t)stream>>>(in, out, count);
+  MB_CUDA(cudaGetLastError());
+  count_launches(1);
+  return 0;
+}
+
+// fp8 scales times 2^8 (fp16) or 2^120 (bf16), rounded to the scales' own type; out may be in.
+extern "C" int marlin_b200_fp8_fuse_exponent_bias(const void* in, void* out, int64_t count, int act_dtype,
+                                                  void* stream) {
+  MB_CHECK(count >= 0, "negative size");
+  MB_CHECK(act_dtype == MARLIN_B200_F16 || act_dtype == MARLIN_B200_BF16, "scales must be fp16 or bf16");
+  if (count == 0) return 0;
+  MB_CHECK(in != nullptr && out != nullptr, "null tensor pointer");
+  auto s = (cudaStream_t)stream;
+  if (act_dtype == MARLIN_B200_F16)
+    fp8_fuse_bias_kernel<__half><<<elementwise_grid(count), 256, 0, s>>>((const __half*)in, (__half*)out, count, 256.f);
+  else
+    fp8_fuse_bias_kernel<__nv_bfloat16><<<elementwise_grid(count), 256, 0, s>>>(
+        (const __nv_bfloat16*)in, (__nv_bfloat16*)out, count, 1.329227995784916e36f);   // 2^120
+  MB_CUDA(cudaGetLastError());
+  count_launches(1);
+  return 0;
+}
 
 extern "C" int marlin_b200_int4_fp8_preprocess(const int32_t* qweight, const int32_t* qzeros, int32_t* out,
                                                int64_t rows, int64_t words_per_row, int64_t zero_rows,

@@ -118,6 +118,123 @@ def awq_marlin_repack(b_q_weight: torch.Tensor, size_k: int, size_n: int, num_bi
     return out
 
 
+def _moe_repack_checks(b_q_weight: torch.Tensor, size_k: int, size_n: int, num_bits: int, is_a_8bit: bool) -> int:
+    _check(not is_a_8bit, "is_a_8bit=True (8-bit activation layout) is not supported")
+    _check(num_bits in (4, 8), f"num_bits must be 4 or 8. Got = {num_bits}")
+    _check(b_q_weight.is_cuda and b_q_weight.is_contiguous() and b_q_weight.dtype == torch.int32,
+           "b_q_weight must be a contiguous int32 GPU tensor")
+    _check(b_q_weight.dim() == 3, "b_q_weight must be [num_experts, ...]")
+    _check(size_k % 16 == 0, f"size_k = {size_k} is not divisible by tile_k_size = 16")
+    _check(size_n % 64 == 0, f"size_n = {size_n} is not divisible by tile_n_size = 64")
+    return b_q_weight.shape[0]
+
+
+def gptq_marlin_moe_repack(b_q_weight: torch.Tensor, perm: torch.Tensor | None, size_k: int, size_n: int,
+                           num_bits: int, is_a_8bit: bool = False) -> torch.Tensor:
+    """All experts of a layer in one launch (the reference loops over the experts in Python:
+    vllm/_custom_ops.py:1228-1247).  b_q_weight [E, K / pack_factor, N], perm [E, K] (or empty)."""
+    lib = _lib.load()
+    e = _moe_repack_checks(b_q_weight, size_k, size_n, num_bits, is_a_8bit)
+    pf = 32 // num_bits
+    _check(tuple(b_q_weight.shape[1:]) == (size_k // pf, size_n),
+           f"Shape mismatch: b_q_weight = {tuple(b_q_weight.shape)}, size_k = {size_k}, size_n = {size_n}, "
+           f"pack_factor = {pf}")
+    has_perm = perm is not None and perm.numel() > 0
+    if has_perm:
+        _check(perm.is_cuda and perm.is_contiguous() and perm.dtype == torch.int32,
+               "perm must be a contiguous int32 GPU tensor")
+        _check(perm.numel() == e * size_k, f"perm.numel() = {perm.numel()} is not num_experts * size_k")
+    with torch.cuda.device(b_q_weight.device):
+        out = torch.empty((e, size_k // 16, size_n * 16 // pf), dtype=torch.int32, device=b_q_weight.device)
+        _lib.check(lib.marlin_b200_gptq_moe_repack(_ptr(b_q_weight), _ptr(perm) if has_perm else None, _ptr(out),
+                                                   e, size_k, size_n, num_bits, _stream(b_q_weight.device)))
+    return out
+
+
+def awq_marlin_moe_repack(b_q_weight: torch.Tensor, perm: torch.Tensor | None, size_k: int, size_n: int,
+                          num_bits: int, is_a_8bit: bool = False) -> torch.Tensor:
+    """All experts of a layer in one launch (vllm/_custom_ops.py:1250-1269; `perm` is unused there too).
+    b_q_weight [E, K, N / pack_factor]."""
+    lib = _lib.load()
+    e = _moe_repack_checks(b_q_weight, size_k, size_n, num_bits, is_a_8bit)
+    pf = 32 // num_bits
+    _check(tuple(b_q_weight.shape[1:]) == (size_k, size_n // pf),
+           f"Shape mismatch: b_q_weight = {tuple(b_q_weight.shape)}, size_k = {size_k}, size_n = {size_n}, "
+           f"pack_factor = {pf}")
+    with torch.cuda.device(b_q_weight.device):
+        out = torch.empty((e, size_k // 16, size_n * 16 // pf), dtype=torch.int32, device=b_q_weight.device)
+        _lib.check(lib.marlin_b200_awq_moe_repack(_ptr(b_q_weight), _ptr(out), e, size_k, size_n, num_bits,
+                                                  _stream(b_q_weight.device)))
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# scale re-encoders of fp4 / fp8 checkpoints (eager PyTorch in the reference's loaders)
+# --------------------------------------------------------------------------------------------
+
+def nvfp4_marlin_process_scales(marlin_scales: torch.Tensor, scale_factor: float | None = None,
+                                a_dtype: torch.dtype | None = None) -> tuple[torch.Tensor, float]:
+    """nvfp4 block scales [G, N] -> (the S0E5M3 bytes `marlin_gemm` reads, as float8_e4m3fn; scale_factor).
+    Mirrors nvfp4_marlin_process_scales (marlin_utils_fp4.py:53-112): [0,2,1,3] interleave per four columns,
+    optional power-of-two rescale so that every non-zero scale * 2^7 >= 2 (computed here when `scale_factor`
+    is None and the activations are not fp16; the caller divides the global scale by it)."""
+    import math
+    lib = _lib.load()
+    _check(marlin_scales.is_cuda and marlin_scales.dim() == 2, "marlin_scales must be a 2-D GPU tensor")
+    _check(marlin_scales.size(1) % 4 == 0, "scale columns must be a multiple of 4")
+    half = marlin_scales.to(torch.float16).contiguous()
+    dev = half.device
+    with torch.cuda.device(dev):
+        if scale_factor is None:
+            scale_factor = 1.0
+            if not (a_dtype is not None and a_dtype == torch.float16):
+                mn = torch.empty(1, dtype=torch.float32, device=dev)
+                _lib.check(lib.marlin_b200_nvfp4_scale_min(_ptr(half), half.numel(), _ptr(mn), _stream(dev)))
+                mn = float(mn.item())
+                if math.isfinite(mn) and mn < 2:
+                    scale_factor = float(2.0 ** math.ceil(math.log2(2.0 / mn)))
+        out = torch.empty(half.shape, dtype=torch.uint8, device=dev)
+        _lib.check(lib.marlin_b200_nvfp4_process_scales(_ptr(half), _ptr(out), half.size(0), half.size(1),
+                                                        float(scale_factor), _stream(dev)))
+    return out.view(torch.float8_e4m3fn), float(scale_factor)
+
+
+def nvfp4_marlin_process_global_scale(global_scale: torch.Tensor, a_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """global_scale * 2^(bias - 7), bias = 14 (fp16) / 126 (bf16) (marlin_utils_fp4.py:132-144); a scalar."""
+    a_dtype = global_scale.dtype if a_dtype is None else a_dtype
+    _check(a_dtype in (torch.float16, torch.bfloat16), "activations must be fp16 or bf16")
+    return global_scale * (2.0 ** ((14 if a_dtype == torch.float16 else 126) - 7))
+
+
+def mxfp4_marlin_process_scales(marlin_scales: torch.Tensor, input_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """The reference's Marlin-side form of mxfp4 scales for 16-bit activations: [0,2,1,3] interleave per four
+    columns, as float8_e8m0fnu (marlin_utils_fp4.py:115-129).  `marlin_gemm` of this library takes mxfp4
+    scales in natural column order; this is for callers that hold or exchange the reference's form."""
+    lib = _lib.load()
+    _check(input_dtype is None or input_dtype.itemsize == 2, "only 16-bit activations are supported")
+    _check(marlin_scales.is_cuda and marlin_scales.dim() == 2 and marlin_scales.size(1) % 4 == 0,
+           "marlin_scales must be a 2-D GPU tensor with a multiple of 4 columns")
+    e8 = marlin_scales if marlin_scales.dtype == torch.float8_e8m0fnu else marlin_scales.to(torch.float8_e8m0fnu)
+    e8 = e8.contiguous().view(torch.uint8)
+    out = torch.empty_like(e8)
+    with torch.cuda.device(e8.device):
+        _lib.check(lib.marlin_b200_interleave_scale_bytes(_ptr(e8), _ptr(out), e8.size(0), e8.size(1),
+                                                          _stream(e8.device)))
+    return out.view(torch.float8_e8m0fnu)
+
+
+def fp8_fused_exponent_bias_into_scales(scales: torch.Tensor) -> torch.Tensor:
+    """scales * 2^8 (fp16) / 2^120 (bf16) in the scales' own dtype (marlin_utils_fp8.py:28-39)."""
+    lib = _lib.load()
+    _check(scales.is_cuda and scales.dtype in (torch.float16, torch.bfloat16), "scales must be fp16 / bf16 on the GPU")
+    src = scales.contiguous()
+    out = torch.empty_like(src)
+    with torch.cuda.device(src.device):
+        _lib.check(lib.marlin_b200_fp8_fuse_exponent_bias(_ptr(src), _ptr(out), src.numel(), _act_code(src.dtype),
+                                                          _stream(src.device)))
+    return out
+
+
 def gptq_marlin_moe_repack(b_q_weight: torch.Tensor, perm: torch.Tensor, size_k: int, size_n: int,
                            num_bits: int, is_a_8bit: bool = False) -> torch.Tensor:
     """Per-expert repack of ``[E, K/pf, N]`` (reference: vllm/_custom_ops.py:1228-1249)."""
