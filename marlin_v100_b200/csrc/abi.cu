@@ -197,7 +197,8 @@ extern "C" int marlin_b200_gemm(const void* a, void* c, const int32_t* b_q_weigh
   return dispatch(g);
 }
 
-extern "C" int64_t marlin_b200_moe_gemm_scratch_bytes(int64_t num_sorted, int64_t size_n, int64_t size_k, int) {
+extern "C" int64_t marlin_b200_moe_gemm_scratch_bytes(int64_t num_sorted, int64_t size_n, int64_t size_k, int format) {
+  if (format & MARLIN_B200_FMT_PREPARED) return gemm_stream_i8_grouped_scratch_bytes(num_sorted, size_n, size_k);
   if (size_n % 256 != 0 || size_k % 64 != 0) return 0;  // served by the shape-agnostic kernel
   // the routed rows in sorted order, then the tile list (one entry per block of at least 8 routes)
   return ((num_sorted * size_k * 2 + 255) & ~(int64_t)255) + (num_sorted / 8 + 64) * 4;
@@ -221,8 +222,8 @@ extern "C" int marlin_b200_moe_gemm(const void* a, void* c, const int32_t* b_q_w
   g.topk_weights = topk_weights; g.num_sorted = num_sorted; g.num_experts = num_experts;
   g.block_size = moe_block_size; g.top_k = top_k; g.mul_topk = mul_topk_weights;
   g.scratch = scratch; g.scratch_bytes = scratch_bytes; g.stream = (cudaStream_t)stream;
-  MB_CHECK((format & MARLIN_B200_FMT_PREPARED) == 0,
-           "the grouped GEMM takes expert weights in the reference layout, not the streaming layout");
+  g.prepared = (format & MARLIN_B200_FMT_PREPARED) != 0;
+  g.format = format & ~MARLIN_B200_FMT_PREPARED;
   if (moe_block_size != 8) {
     MB_CHECK(moe_block_size % 16 == 0 && moe_block_size >= 16 && moe_block_size <= 64,
              "unsupported moe_block_size=%d", moe_block_size);
@@ -236,6 +237,14 @@ extern "C" int marlin_b200_moe_gemm(const void* a, void* c, const int32_t* b_q_w
   MB_CHECK(!mul_topk_weights || topk_weights != nullptr, "mul_topk_weights needs topk_weights");
   MB_CHECK(size_m * top_k < (1ll << 31), "size_m * top_k does not fit 32-bit route ids");
   if (g.size_m == 0 || g.size_n == 0 || num_sorted == 0) return 0;
+  if (g.prepared) {
+    // expert weights in the streaming layout: served by the decode-sized integer-MMA kernel only
+    MB_CHECK(gemm_stream_i8_grouped_accepts(g),
+             "expert weights in the streaming layout are served for uint4 / uint4b8, moe_block_size 8 or 16, "
+             "size_k %% 128 == 0, size_n %% 256 == 0, group size a multiple of 128 (or per channel) and a scratch "
+             "buffer of marlin_b200_moe_gemm_scratch_bytes; pass the reference layout otherwise");
+    return launch_gemm_stream_i8_grouped(g);
+  }
   const int rc = launch_gemm_tc(g);  // tensor-memory grouped kernel when the shape qualifies
   if (rc <= 0) return rc;
   return launch_gemm_generic(g);

@@ -110,6 +110,17 @@ struct I8Params {
   int num_ctas;
   int split;
   uint32_t tx_bytes;        // bytes of the small operands of a chunk
+  // grouped (expert) form: a "column group" is (block of NTOK sorted routes, 256 columns of the block's expert)
+  const int32_t* sorted_ids;    // [row_capacity] route ids in expert order, >= num_routes for padding
+  const int32_t* expert_ids;    // [row_capacity / NTOK] expert of every block (-1: not on this rank)
+  const int32_t* num_post_pad;  // [1] sorted rows in use (a multiple of NTOK)
+  const float* topk_weights;    // [num_routes] or NULL
+  int num_routes;               // size_m * top_k
+  int row_capacity;             // rows of the digit planes and the row factors
+  int sum_stride;               // row stride of the digit sums (row capacity rounded up to 16)
+  int ngc;                      // column groups per expert
+  int rows_per_expert;          // scale rows per expert
+  int mul_topk;
 };
 
 __device__ int g_si8_status = 0;
@@ -172,11 +183,15 @@ __host__ __device__ inline int digit_pos(int k_local) {
 // GEMM and the GEMM of this call can start beside them.
 constexpr int AD_THREADS = 128;
 
-template <typename T>
+// GROUPED: one block row per sorted route (grid.x = row capacity); row r converts activation row
+// sorted_ids[r] / top_k; padding entries and rows beyond *num_post_pad are left alone (their outputs are dropped).
+template <typename T, bool GROUPED>
 __global__ void __launch_bounds__(AD_THREADS, 16) act_digits_kernel(const T* __restrict__ a, int64_t a_stride, int M, int K,
                                                          int8_t* __restrict__ digits, float* __restrict__ row_scale,
                                                          float* __restrict__ chunk_sums, int* __restrict__ counters,
-                                                         int num_counters) {
+                                                         int num_counters, const int32_t* __restrict__ sorted_ids,
+                                                         const int32_t* __restrict__ num_post_pad, int top_k,
+                                                         int num_routes, int sum_stride) {
   // grid (token rows, parts): every block finds the maximum of its whole row (the row is small and cached), then
   // converts its own part of the row, so that the conversion of a row is spread over several SMs
   const int m = blockIdx.x, tid = threadIdx.x, ntok = gridDim.x;
@@ -193,15 +208,22 @@ __global__ void __launch_bounds__(AD_THREADS, 16) act_digits_kernel(const T* __r
   __shared__ float s_max;
   const int vecs = K / 8;
   const int v_begin = part * (vecs / parts), v_end = v_begin + vecs / parts;   // a multiple of 16 vectors (one chunk)
-  if (m >= M) {
+  int src_row = m;
+  if constexpr (GROUPED) {
+    if (m >= *num_post_pad) return;
+    const int sid = sorted_ids[m];
+    if (sid >= num_routes) return;
+    src_row = sid / top_k;
+  }
+  if (!GROUPED && m >= M) {
     for (int v = v_begin + tid; v < v_end; v += AD_THREADS)
 #pragma unroll
       for (int d = 0; d < NDIG; ++d) *reinterpret_cast<uint2*>(digits + (int64_t)(d * ntok + m) * K + v * 8) = make_uint2(0, 0);
-    for (int c = v_begin / 16 + tid; c < v_end / 16; c += AD_THREADS) chunk_sums[c * ntok + m] = 0.f;
+    for (int c = v_begin / 16 + tid; c < v_end / 16; c += AD_THREADS) chunk_sums[c * sum_stride + m] = 0.f;
     if (tid == 0 && part == 0) row_scale[m] = 0.f;
     return;
   }
-  const T* row = a + (int64_t)m * a_stride;
+  const T* row = a + (int64_t)src_row * a_stride;
   float mx = 0.f;
   for (int v = tid; v < vecs; v += AD_THREADS) {
     const uint4 q = *reinterpret_cast<const uint4*>(row + v * 8);
@@ -262,11 +284,11 @@ __global__ void __launch_bounds__(AD_THREADS, 16) act_digits_kernel(const T* __r
     // the 16 vectors of a chunk sit in 16 consecutive lanes
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (v < v_end && (tid & 15) == 0) chunk_sums[(v >> 4) * ntok + m] = sum;
+    if (v < v_end && (tid & 15) == 0) chunk_sums[(v >> 4) * sum_stride + m] = sum;
   }
 }
 
-template <typename T, int FMT, int TOKH>
+template <typename T, int FMT, int TOKH, bool GROUPED>
 __global__ void __launch_bounds__(Cfg<TOKH>::THREADS, 1)
 stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmS,
                  const __grid_constant__ CUtensorMap tmZ, const I8Params p) {
@@ -296,14 +318,25 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // come first so that their cross-CTA sums are formed while every CTA still streams.
   __shared__ int s_run_g[3], s_run_c[3], s_run_len[3];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int64_t U = (int64_t)p.ng * p.kc;
-  int64_t u0, u1;
-  if (p.split) {
-    u0 = range_start(blockIdx.x, U, p.num_ctas);
-    u1 = range_start(blockIdx.x + 1, U, p.num_ctas);
-  } else {
-    u0 = range_start(blockIdx.x, p.ng, p.num_ctas) * p.kc;
-    u1 = range_start(blockIdx.x + 1, p.ng, p.num_ctas) * p.kc;
+  int ng_total = p.ng;
+  if constexpr (GROUPED) {
+    // the block count comes from the routing kernels in front: nothing is read before they have completed
+    pdl_wait_prior_grid();
+    ng_total = (*p.num_post_pad / NTOK) * p.ngc;
+  }
+  const int64_t U = (int64_t)ng_total * p.kc;
+  // every CTA that takes part owns at least one unit (the owners of a group are then consecutive CTAs); in the
+  // grouped form the unit count is only known here, so the surplus CTAs of the launch stay idle
+  const int num_ctas = (int)((U < p.num_ctas) ? (U > 0 ? U : 1) : p.num_ctas);
+  int64_t u0 = 0, u1 = 0;
+  if ((int)blockIdx.x < num_ctas) {
+    if (p.split) {
+      u0 = range_start(blockIdx.x, U, num_ctas);
+      u1 = range_start(blockIdx.x + 1, U, num_ctas);
+    } else {
+      u0 = range_start(blockIdx.x, ng_total, num_ctas) * p.kc;
+      u1 = range_start(blockIdx.x + 1, ng_total, num_ctas) * p.kc;
+    }
   }
   const int total = (int)(u1 - u0);
   if (tid == 0) {
@@ -358,10 +391,22 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int r = 0; r < 3 && ok; ++r) {
         const uint8_t* src = p.w + ((int64_t)s_run_g[r] * p.kc + s_run_c[r]) * RAW_BYTES;   // a run is linear
         const int len = s_run_len[r];
+        int g = s_run_g[r], c = s_run_c[r];
         for (int j = 0; j < len; ++j, ++i) {
           if (i >= STAGES && !mbar_wait_park(raw_free(s), ph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 1); ok = false; break; }
           mbar_arrive_expect_tx(full(s), RAW_BYTES);
-          bulk_load(base + s * STAGE_BYTES, src + (int64_t)j * RAW_BYTES, RAW_BYTES, full(s));
+          if constexpr (GROUPED) {
+            // group g = (block, column group of the block's expert): linear inside the group only
+            if (j == 0 || c == 0) {
+              int e = p.expert_ids[g / p.ngc];
+              if (e < 0) e = 0;   // a block of an expert that is not here: any weights do, its rows are dropped
+              src = p.w + (((int64_t)e * p.ngc + g % p.ngc) * p.kc) * RAW_BYTES;
+            }
+            bulk_load(base + s * STAGE_BYTES, src + (int64_t)c * RAW_BYTES, RAW_BYTES, full(s));
+            if (++c == p.kc) { c = 0; ++g; }
+          } else {
+            bulk_load(base + s * STAGE_BYTES, src + (int64_t)j * RAW_BYTES, RAW_BYTES, full(s));
+          }
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
       }
@@ -380,11 +425,22 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (i >= STAGES && !mbar_wait_park(empty(s), ph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 9); ok = false; break; }
         const uint32_t st = base + s * STAGE_BYTES;
         mbar_arrive_expect_tx(fullm(s), p.tx_bytes);
-        tma_load_2d(st + OFF_ACT, &tmA, fullm(s), c * KCH, 0);
-        bulk_load(st + OFF_SA, p.chunk_sums + (int64_t)c * NTOK, NTOK * 4, fullm(s));
-        const int srow = (p.num_groups == 1) ? 0 : c / p.cps;
-        tma_load_2d(st + OFF_S, &tmS, fullm(s), g * kGroupN, srow);
-        if constexpr (format_has_zp(FMT)) tma_load_2d(st + OFF_Z, &tmZ, fullm(s), g * kGroupN, srow);
+        int srow = (p.num_groups == 1) ? 0 : c / p.cps;
+        int col = g * kGroupN;
+        if constexpr (GROUPED) {
+          const int blk = g / p.ngc;
+          int e = p.expert_ids[blk];
+          if (e < 0) e = 0;
+          tma_load_3d(st + OFF_ACT, &tmA, fullm(s), c * KCH, blk * NTOK, 0);   // both digit planes of the block's rows
+          bulk_load(st + OFF_SA, p.chunk_sums + (int64_t)c * p.sum_stride + blk * NTOK, NTOK * 4, fullm(s));
+          srow += e * p.rows_per_expert;
+          col = (g % p.ngc) * kGroupN;
+        } else {
+          tma_load_2d(st + OFF_ACT, &tmA, fullm(s), c * KCH, 0);
+          bulk_load(st + OFF_SA, p.chunk_sums + (int64_t)c * NTOK, NTOK * 4, fullm(s));
+        }
+        tma_load_2d(st + OFF_S, &tmS, fullm(s), col, srow);
+        if constexpr (format_has_zp(FMT)) tma_load_2d(st + OFF_Z, &tmZ, fullm(s), col, srow);
         if (++c == p.kc) { c = 0; ++g; }
         if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
@@ -486,6 +542,28 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (seg_end) {
         const bool whole = (seg_c0 == 0) && (c == p.kc - 1);
         if (first_segment) pdl_wait_prior_grid();   // the row factors come from the kernel in front
+        if constexpr (GROUPED) {
+          const int blk = g / p.ngc, e = p.expert_ids[blk];
+          const int n = (g % p.ngc) * kGroupN + nl;
+          if (ok && s_abort == 0) {
+            if (whole) {
+              const float bv = (bias != nullptr && e >= 0) ? to_float<T>(bias[(int64_t)e * p.N + bias_index(n)]) : 0.f;
+#pragma unroll
+              for (int m = 0; m < NTOK; ++m) {
+                const int sid = p.sorted_ids[blk * NTOK + m];
+                if (sid < p.num_routes && e >= 0) {
+                  float v = fmaf(acc[m], p.row_scale[blk * NTOK + m], bv);
+                  if (p.mul_topk) v *= p.topk_weights[sid];
+                  Cout[(int64_t)sid * p.N + n] = from_float<T>(v);
+                }
+              }
+            } else {
+              float* P = p.partials + ((int64_t)blockIdx.x * 2 + (seg_c0 == 0 ? 1 : 0)) * (NTOK * kGroupN);
+#pragma unroll
+              for (int m = 0; m < NTOK; ++m) P[m * kGroupN + nl] = acc[m] * p.row_scale[blk * NTOK + m];
+            }
+          }
+        } else {
         const int n = g * kGroupN + nl;
         if (ok && s_abort == 0) {
           if (whole) {
@@ -500,6 +578,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int m = 0; m < NTOK; ++m)
               if (m < p.M) P[m * kGroupN + nl] = acc[m] * p.row_scale[m];
           }
+        }
         }
         if (!whole) {   // runs 0 and 1: the reduce warp takes it from here
           __syncwarp();
@@ -526,7 +605,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!mbar_wait_park(part_ready(r), 0, &s_abort, 2000)) { atomicExch(&g_si8_status, 10); break; }
       if (!waited) { pdl_wait_prior_grid(); waited = true; }   // the counters were cleared by the kernel in front
       const int64_t ua = (int64_t)g * p.kc;
-      const int64_t pa = unit_owner(ua, U, p.num_ctas), pb = unit_owner(ua + p.kc - 1, U, p.num_ctas);
+      const int64_t pa = unit_owner(ua, U, num_ctas), pb = unit_owner(ua + p.kc - 1, U, num_ctas);
       if (rt == 0) {
         int last = 0;
         if (s_abort == 0) {
@@ -543,7 +622,10 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr int64_t SLOT = NTOK * kGroupN;
       // the first owner holds the group's first chunks (slot 1), every other one a run from midway (slot 0)
       const float4* first = reinterpret_cast<const float4*>(p.partials + (pa * 2 + 1) * SLOT);
-      const int total4 = p.M * (kGroupN / 4);
+      const int total4 = (GROUPED ? NTOK : p.M) * (kGroupN / 4);
+      const int blk = GROUPED ? g / p.ngc : 0;
+      const int ex = GROUPED ? p.expert_ids[blk] : 0;
+      const int gcol = GROUPED ? g % p.ngc : g;
       for (int e0 = rt; e0 < total4; e0 += 128 * 4) {
         float4 sum[4];
 #pragma unroll
@@ -569,18 +651,26 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int e = e0 + 128 * uu;
           if (e < total4) {
             const int m = e / (kGroupN / 4), col = (e % (kGroupN / 4)) * 4;
-            const int nn = g * kGroupN + col;
+            const int nn = gcol * kGroupN + col;
+            int64_t out_row = m;
+            float wgt = 1.f;
+            if constexpr (GROUPED) {
+              const int sid = p.sorted_ids[blk * NTOK + m];
+              if (sid >= p.num_routes || ex < 0) continue;
+              out_row = sid;
+              if (p.mul_topk) wgt = p.topk_weights[sid];
+            }
             float bv[4] = {0.f, 0.f, 0.f, 0.f};
             if (bias != nullptr) {
 #pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4) bv[q4] = to_float<T>(bias[bias_index(nn + q4)]);
+              for (int q4 = 0; q4 < 4; ++q4) bv[q4] = to_float<T>(bias[(GROUPED ? (int64_t)ex * p.N : 0) + bias_index(nn + q4)]);
             }
             T o4[4];
-            o4[0] = from_float<T>(sum[uu].x + bv[0]);
-            o4[1] = from_float<T>(sum[uu].y + bv[1]);
-            o4[2] = from_float<T>(sum[uu].z + bv[2]);
-            o4[3] = from_float<T>(sum[uu].w + bv[3]);
-            *reinterpret_cast<uint2*>(Cout + (int64_t)m * p.N + nn) = *reinterpret_cast<const uint2*>(o4);
+            o4[0] = from_float<T>((sum[uu].x + bv[0]) * wgt);
+            o4[1] = from_float<T>((sum[uu].y + bv[1]) * wgt);
+            o4[2] = from_float<T>((sum[uu].z + bv[2]) * wgt);
+            o4[3] = from_float<T>((sum[uu].w + bv[3]) * wgt);
+            *reinterpret_cast<uint2*>(Cout + out_row * p.N + nn) = *reinterpret_cast<const uint2*>(o4);
           }
         }
       }
@@ -694,8 +784,9 @@ int launch_one(const GemmArgs& g) {
     cfg.stream = g.stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    MB_CUDA(cudaLaunchKernelEx(&cfg, act_digits_kernel<T>, reinterpret_cast<const T*>(g.a), g.a_stride, m, (int)K, digits,
-                               row_scale, chunk_sums, p.counters, p.ng));
+    MB_CUDA(cudaLaunchKernelEx(&cfg, act_digits_kernel<T, false>, reinterpret_cast<const T*>(g.a), g.a_stride, m, (int)K,
+                               digits, row_scale, chunk_sums, p.counters, p.ng, (const int32_t*)nullptr,
+                               (const int32_t*)nullptr, 1, 0, NTOK));
     count_launches(1);
   }
   CUtensorMap tmA, tmS, tmZ;
@@ -725,7 +816,7 @@ int launch_one(const GemmArgs& g) {
   int dev = 0;
   MB_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !attr_set[dev]) {
-    MB_CUDA(cudaFuncSetAttribute(stream_i8_kernel<T, FMT, TOKH>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    MB_CUDA(cudaFuncSetAttribute(stream_i8_kernel<T, FMT, TOKH, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -735,9 +826,117 @@ int launch_one(const GemmArgs& g) {
   cfg.stream = g.stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  MB_CUDA(cudaLaunchKernelEx(&cfg, stream_i8_kernel<T, FMT, TOKH>, tmA, tmS, tmZ, p));
+  MB_CUDA(cudaLaunchKernelEx(&cfg, stream_i8_kernel<T, FMT, TOKH, false>, tmA, tmS, tmZ, p));
   count_launches(1);
   return 0;
+}
+
+// ---- grouped (expert) form --------------------------------------------------------------------------------
+// scratch: counters | partial sums | digit planes [2][rows][K] | row factors [rows] | digit sums [K / 128][rows]
+int64_t grouped_counters_bytes(int64_t rows, int64_t n) { return ((rows / 8) * (n / kGroupN) * 4 + 255) & ~(int64_t)255; }
+
+template <typename T, int FMT, int TOKH>
+int launch_grouped(const GemmArgs& g) {
+  using C = Cfg<TOKH>;
+  constexpr int NTOK = C::NTOK;
+  const int64_t K = g.size_k, N = g.size_n, R = g.num_sorted;
+  I8Params p{};
+  p.w = reinterpret_cast<const uint8_t*>(g.bq);
+  p.c = g.c; p.bias = g.bias;
+  p.M = (int)g.size_m; p.N = (int)N; p.K = (int)K;
+  p.num_groups = (int)g.num_groups;
+  p.kc = (int)(K / KCH);
+  p.ngc = (int)(N / kGroupN);
+  p.ng = 0;
+  p.cps = (g.num_groups == 1) ? p.kc : (int)((K / g.num_groups) / KCH);
+  p.rows_per_expert = (int)g.num_groups;
+  p.sorted_ids = g.sorted_ids; p.expert_ids = g.expert_ids; p.num_post_pad = g.num_post_pad;
+  p.topk_weights = g.topk_weights; p.mul_topk = g.mul_topk;
+  p.num_routes = (int)(g.size_m * g.top_k);
+  p.row_capacity = (int)R;
+  p.sum_stride = (int)((R + 15) & ~(int64_t)15);
+  uint8_t* sc = reinterpret_cast<uint8_t*>(g.scratch);
+  const int64_t cb = grouped_counters_bytes(R, N), pb = partial_bytes();
+  p.counters = reinterpret_cast<int*>(sc);
+  p.partials = reinterpret_cast<float*>(sc + cb);
+  int8_t* digits = reinterpret_cast<int8_t*>(sc + cb + pb);
+  const int64_t digit_bytes = (2 * R * K + 255) & ~(int64_t)255;
+  float* row_scale = reinterpret_cast<float*>(digits + digit_bytes);
+  float* chunk_sums = row_scale + ((R + 63) & ~(int64_t)63);
+  p.row_scale = row_scale;
+  p.chunk_sums = chunk_sums;
+  p.split = 1;
+  p.num_ctas = sm_count();
+  p.tx_bytes = C::ACT_BYTES + NTOK * 4 + kGroupN * 2 * (format_has_zp(FMT) ? 2 : 1);
+
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  int parts = 1;
+  while (parts < 4 && K % (KCH * parts * 2) == 0 && K / (parts * 2) >= 8 * AD_THREADS) parts *= 2;
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)R, parts);
+    cfg.blockDim = dim3(AD_THREADS);
+    cfg.stream = g.stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int num_counters = (int)((R / NTOK) * p.ngc);
+    MB_CUDA(cudaLaunchKernelEx(&cfg, act_digits_kernel<T, true>, reinterpret_cast<const T*>(g.a), g.a_stride, (int)g.size_m,
+                               (int)K, digits, row_scale, chunk_sums, p.counters, num_counters, g.sorted_ids,
+                               g.num_post_pad, g.top_k, p.num_routes, p.sum_stride));
+    count_launches(1);
+  }
+  CUtensorMap tmA, tmS, tmZ;
+  {
+    const uint64_t dims[2] = {(uint64_t)N, (uint64_t)(g.num_groups * g.num_experts)};
+    const uint64_t strides[1] = {(uint64_t)N * 2};
+    const uint32_t box[2] = {kGroupN, 1};
+    if (int rc = cached_tensor_map(&tmS, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, g.scales, dims, strides, box,
+                                   CU_TENSOR_MAP_SWIZZLE_NONE))
+      return rc;
+    tmZ = tmS;
+    if (format_has_zp(FMT)) {
+      if (int rc = cached_tensor_map(&tmZ, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, g.zeros, dims, strides, box,
+                                     CU_TENSOR_MAP_SWIZZLE_NONE))
+        return rc;
+    }
+  }
+  {
+    // digit planes [2][rows][K]: one box = both planes of a block's rows over one 128-k chunk
+    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)R, 2};
+    const uint64_t strides[2] = {(uint64_t)K, (uint64_t)R * K};
+    const uint32_t box[3] = {KCH, (uint32_t)NTOK, 2};
+    if (int rc = cached_tensor_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, digits, dims, strides, box,
+                                   CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  static bool attr_set[64] = {};
+  int dev = 0;
+  MB_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    MB_CUDA(cudaFuncSetAttribute(stream_i8_kernel<T, FMT, TOKH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.num_ctas);
+  cfg.blockDim = dim3(C::THREADS);
+  cfg.dynamicSmemBytes = C::SMEM;
+  cfg.stream = g.stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MB_CUDA(cudaLaunchKernelEx(&cfg, stream_i8_kernel<T, FMT, TOKH, true>, tmA, tmS, tmZ, p));
+  count_launches(1);
+  return 0;
+}
+
+template <typename T>
+int launch_grouped_dtype(const GemmArgs& g) {
+  switch (g.format) {
+    case kU4B8: return g.block_size == 8 ? launch_grouped<T, kU4B8, 1>(g) : launch_grouped<T, kU4B8, 2>(g);
+    case kU4: return g.block_size == 8 ? launch_grouped<T, kU4, 1>(g) : launch_grouped<T, kU4, 2>(g);
+  }
+  return 1;
 }
 
 template <typename T>
@@ -764,6 +963,29 @@ bool gemm_stream_i8_accepts(const GemmArgs& g) {
   if (g.num_groups > 1 && (g.size_k / g.num_groups) % KCH != 0) return false;
   if (g.global_scale != nullptr) return false;
   return g.scratch != nullptr && g.scratch_bytes >= gemm_stream_i8_scratch_bytes(g.size_m, g.size_n, g.size_k);
+}
+
+// grouped form: expert weights [E][...] in the streaming layout, blocks of 8 or 16 sorted routes
+int64_t gemm_stream_i8_grouped_scratch_bytes(int64_t num_sorted, int64_t n, int64_t k) {
+  if (num_sorted <= 0 || !stream::layout_accepts(k, n)) return 0;
+  return grouped_counters_bytes(num_sorted, n) + partial_bytes() + ((2 * num_sorted * k + 255) & ~(int64_t)255) +
+         ((num_sorted + 63) & ~(int64_t)63) * 4 + (k / KCH) * ((num_sorted + 15) & ~(int64_t)15) * 4 + 256;
+}
+
+bool gemm_stream_i8_grouped_accepts(const GemmArgs& g) {
+  if (g.sorted_ids == nullptr || !g.prepared) return false;
+  if (g.format != kU4B8 && g.format != kU4) return false;
+  if (g.block_size != 8 && g.block_size != 16) return false;
+  if (g.num_sorted < g.block_size || !stream::layout_accepts(g.size_k, g.size_n)) return false;
+  if (g.num_groups > 1 && (g.size_k / g.num_groups) % KCH != 0) return false;
+  if (g.global_scale != nullptr) return false;
+  return g.scratch != nullptr &&
+         g.scratch_bytes >= gemm_stream_i8_grouped_scratch_bytes(g.num_sorted, g.size_n, g.size_k);
+}
+
+int launch_gemm_stream_i8_grouped(const GemmArgs& g) {
+  if (g.act_dtype == MARLIN_B200_F16) return launch_grouped_dtype<__half>(g);
+  return launch_grouped_dtype<__nv_bfloat16>(g);
 }
 
 int launch_gemm_stream_i8(const GemmArgs& g) {

@@ -624,6 +624,8 @@ def moe_wna16_marlin_gemm(input: torch.Tensor, output: torch.Tensor | None, b_qw
         _check(topk_weights.numel() >= size_m * top_k, "topk_weights has fewer than size_m * top_k entries")
         num_sorted = sorted_token_ids.numel()
 
+        if is_prepared(b_qweight, size_k, size_n):
+            fmt |= _lib.FMT_PREPARED     # expert weights converted by prepare_weights (decode-sized blocks only)
         nbytes = lib.marlin_b200_moe_gemm_scratch_bytes(num_sorted, size_n, size_k, fmt)
         scratch = _scratch(nbytes, a.device)
         _lib.check(lib.marlin_b200_moe_gemm(
