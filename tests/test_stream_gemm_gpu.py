@@ -141,9 +141,13 @@ def test_strided_a_and_preallocated_c():
     check(out, mo.dense_reference(a, qw.deq))
 
 
-def test_grouped_gemm_refuses_the_flag():
+def test_grouped_gemm_takes_the_flag_only_for_decode_blocks():
+    """Expert weights in the streaming layout are served for blocks of 8 / 16 routes (tests/test_moe_stream_gpu.py);
+    any other block size is refused with a message that names the reference layout."""
     from marlin_v100_b200 import _lib
     lib = _lib.load()
-    rc = lib.marlin_b200_moe_gemm(None, None, None, None, None, None, None, None, None, None, None, 16, 1, 16, 1, 0, 0,
+    dev = torch.zeros(4096, dtype=torch.int32, device="cuda")
+    ptr = dev.data_ptr()
+    rc = lib.marlin_b200_moe_gemm(ptr, ptr, ptr, ptr, None, None, None, ptr, ptr, ptr, ptr, 64, 1, 64, 1, 0, 0,
                                   0 | _lib.FMT_PREPARED, 1, 256, 128, 1, None, 0, None)
     assert rc == -1 and b"reference layout" in lib.marlin_b200_last_error()
