@@ -566,8 +566,8 @@ __global__ void __launch_bounds__(GROUP_N) decode_tc_reduce_kernel(const DtParam
   const int64_t U = (int64_t)p.ng * p.kc, P = p.num_ctas;
   const int64_t ua = (int64_t)g * p.kc, ub = ua + p.kc - 1;
   const int64_t pa = ((ua + 1) * P - 1) / U, pb = ((ub + 1) * P - 1) / U;
-  if (pa == pb) return;  // written directly by its only owner
-  pdl_wait_prior_grid();
+  pdl_wait_prior_grid();   // before any return: the grid never retires ahead of the kernel in front
+  if (pa == pb) return;    // written directly by its only owner
   const int col = threadIdx.x;
   const int n = g * GROUP_N + col;
   constexpr int SLOT = 16 * GROUP_N;
@@ -660,7 +660,13 @@ int launch_one(const GemmArgs& g, const void* a, void* c, int m) {
     MB_CUDA(cudaLaunchKernelEx(&cfg, decode_tc_kernel<T, FMT>, tmW, tmA, tmS, tmZ, p));
     count_launches(1);
   }
-  if (U % p.num_ctas != 0 || (U / p.num_ctas) % p.kc != 0) {
+  // the reduce kernel is launched only when some column group really has more than one owner
+  bool any_split = false;
+  for (int64_t gi = 0; gi < p.ng && !any_split; ++gi) {
+    const int64_t ua = gi * p.kc, ub = ua + p.kc - 1;
+    any_split = ((ua + 1) * p.num_ctas - 1) / U != ((ub + 1) * p.num_ctas - 1) / U;
+  }
+  if (any_split) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.ng, m);
     cfg.blockDim = dim3(GROUP_N);
