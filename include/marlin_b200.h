@@ -40,9 +40,16 @@ extern "C" {
 #define MARLIN_B200_FMT_NVFP4 5
 #define MARLIN_B200_FMT_MXFP4 6
 
-/* Flag, or-ed into the `format` argument of marlin_b200_gemm / marlin_b200_gemm_scratch_bytes: b_q_weight is
- * in the library's streaming layout (made by marlin_b200_prepare_weights), not in the reference layout. */
+/* Flag, or-ed into the `format` argument of marlin_b200_gemm / marlin_b200_moe_gemm and their scratch-size
+ * functions: b_q_weight is in the library's streaming layout (made by marlin_b200_prepare_weights), not in the
+ * reference layout.  The grouped GEMM serves such weights for uint4 / uint4b8 with moe_block_size 8 or 16 (the
+ * decode regime); marlin_b200_moe_gemm_scratch_bytes then returns the room for digit planes in sorted order. */
 #define MARLIN_B200_FMT_PREPARED 0x100
+/* Flag for marlin_b200_moe_gemm together with MARLIN_B200_FMT_PREPARED: `a` is the [size_m, 2 * size_k]
+ * gate | up output of the expert layer's first GEMM, and silu(gate) * up (rounded to the activation type where
+ * marlin_b200_silu_and_mul rounds) is what the GEMM multiplies: the second GEMM of the layer without the
+ * separate SiLU-and-mul pass (eager PyTorch in the reference, fused_marlin_moe.py:161-165). */
+#define MARLIN_B200_FMT_SILU_INPUT 0x200
 
 /* Scale element kinds for marlin_b200_format_from_type_id(). */
 #define MARLIN_B200_SCALE_ACT 0  /* same 16-bit type as the activations */

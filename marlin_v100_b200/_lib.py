@@ -68,6 +68,7 @@ SIGNATURES = {
 }
 
 FMT_PREPARED = 0x100  # MARLIN_B200_FMT_PREPARED
+FMT_SILU_INPUT = 0x200  # MARLIN_B200_FMT_SILU_INPUT
 
 _lib = None
 

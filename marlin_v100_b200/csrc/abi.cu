@@ -223,7 +223,10 @@ extern "C" int marlin_b200_moe_gemm(const void* a, void* c, const int32_t* b_q_w
   g.block_size = moe_block_size; g.top_k = top_k; g.mul_topk = mul_topk_weights;
   g.scratch = scratch; g.scratch_bytes = scratch_bytes; g.stream = (cudaStream_t)stream;
   g.prepared = (format & MARLIN_B200_FMT_PREPARED) != 0;
-  g.format = format & ~MARLIN_B200_FMT_PREPARED;
+  g.silu_input = (format & MARLIN_B200_FMT_SILU_INPUT) != 0;
+  g.format = format & ~(MARLIN_B200_FMT_PREPARED | MARLIN_B200_FMT_SILU_INPUT);
+  MB_CHECK(!g.silu_input || g.prepared, "SiLU-and-mul on load is served for expert weights in the streaming layout only");
+  if (g.silu_input) g.a_stride = 2 * size_k;
   if (moe_block_size != 8) {
     MB_CHECK(moe_block_size % 16 == 0 && moe_block_size >= 16 && moe_block_size <= 64,
              "unsupported moe_block_size=%d", moe_block_size);

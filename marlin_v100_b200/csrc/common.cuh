@@ -158,6 +158,7 @@ struct GemmArgs {
   int64_t scratch_bytes;
   cudaStream_t stream;
   bool prepared;  // b_q_weight is in the streaming layout (stream_layout.cuh)
+  bool silu_input;  // grouped, streaming layout: `a` is [size_m, 2 * size_k] gate | up, SiLU-and-mul applied on load
 };
 
 // kernel launchers (one per translation unit)

@@ -185,8 +185,18 @@ constexpr int AD_THREADS = 128;
 
 // GROUPED: one block row per sorted route (grid.x = row capacity); row r converts activation row
 // sorted_ids[r] / top_k; padding entries and rows beyond *num_post_pad are left alone (their outputs are dropped).
-template <typename T, bool GROUPED>
-__global__ void __launch_bounds__(AD_THREADS, 16) act_digits_kernel(const T* __restrict__ a, int64_t a_stride, int M, int K,
+// SILU (grouped form only): the activation rows are the [rows, 2 K] gate | up output of the expert layer's first
+// GEMM and the value converted is silu(gate) * up, rounded to T at the two places where the separate
+// SiLU-and-mul kernel rounds (silu, then the product).
+template <typename T>
+__device__ __forceinline__ float silu_mul_rounded(T gate, T up) {
+  const float x = to_float<T>(gate);
+  const float sl = to_float<T>(from_float<T>(x / (1.f + expf(-x))));
+  return to_float<T>(from_float<T>(sl * to_float<T>(up)));
+}
+
+template <typename T, bool GROUPED, bool SILU = false>
+__global__ void __launch_bounds__(AD_THREADS, GROUPED ? 4 : 16) act_digits_kernel(const T* __restrict__ a, int64_t a_stride, int M, int K,
                                                          int8_t* __restrict__ digits, float* __restrict__ row_scale,
                                                          float* __restrict__ chunk_sums, int* __restrict__ counters,
                                                          int num_counters, const int32_t* __restrict__ sorted_ids,
@@ -228,8 +238,15 @@ __global__ void __launch_bounds__(AD_THREADS, 16) act_digits_kernel(const T* __r
   for (int v = tid; v < vecs; v += AD_THREADS) {
     const uint4 q = *reinterpret_cast<const uint4*>(row + v * 8);
     const T* e = reinterpret_cast<const T*>(&q);
+    if constexpr (SILU) {
+      const uint4 qu = *reinterpret_cast<const uint4*>(row + K + v * 8);
+      const T* eu = reinterpret_cast<const T*>(&qu);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(to_float<T>(e[i])));
+      for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(silu_mul_rounded<T>(e[i], eu[i])));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(to_float<T>(e[i])));
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -258,11 +275,15 @@ __global__ void __launch_bounds__(AD_THREADS, 16) act_digits_kernel(const T* __r
     if (v < v_end) {
       const uint4 q = *reinterpret_cast<const uint4*>(row + v * 8);
       const T* el = reinterpret_cast<const T*>(&q);
+      uint4 qu = make_uint4(0, 0, 0, 0);
+      if constexpr (SILU) qu = *reinterpret_cast<const uint4*>(row + K + v * 8);
+      const T* eu = reinterpret_cast<const T*>(&qu);
       uint32_t out[NDIG][2] = {};
       float s1 = 0.f, s2 = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float x = finite ? to_float<T>(el[i]) * f1 * f2 : 0.f;
+        const float val = SILU ? silu_mul_rounded<T>(el[i], eu[i]) : to_float<T>(el[i]);
+        const float x = finite ? val * f1 * f2 : 0.f;
         const float d1 = rintf(x);
         const float d2 = fminf(fmaxf(rintf((x - d1) * 256.f), -127.f), 127.f);
         s1 += d1; s2 += d2;
@@ -882,7 +903,8 @@ int launch_grouped(const GemmArgs& g) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const int num_counters = (int)((R / NTOK) * p.ngc);
-    MB_CUDA(cudaLaunchKernelEx(&cfg, act_digits_kernel<T, true>, reinterpret_cast<const T*>(g.a), g.a_stride, (int)g.size_m,
+    auto kern = g.silu_input ? act_digits_kernel<T, true, true> : act_digits_kernel<T, true, false>;
+    MB_CUDA(cudaLaunchKernelEx(&cfg, kern, reinterpret_cast<const T*>(g.a), g.a_stride, (int)g.size_m,
                                (int)K, digits, row_scale, chunk_sums, p.counters, num_counters, g.sorted_ids,
                                g.num_post_pad, g.top_k, p.num_routes, p.sum_stride));
     count_launches(1);

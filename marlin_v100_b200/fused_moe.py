@@ -89,7 +89,8 @@ def fused_marlin_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Te
     if workspace is None:
         workspace = torch.empty(0, dtype=torch.int32, device=dev)
 
-    if w1_streaming is not None and w2_streaming is not None and block_size_m <= 16:
+    streaming = w1_streaming is not None and w2_streaming is not None and block_size_m <= 16
+    if streaming:
         w1, w2 = w1_streaming, w2_streaming
     sorted_ids, expert_ids, num_post = moe_align_block_size(topk_ids, block_size_m, global_num_experts,
                                                             expert_map)
@@ -102,8 +103,11 @@ def fused_marlin_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Te
                               None, workspace, sorted_ids, expert_ids, num_post, flat_w, block_size_m,
                               topk, apply_router_weight_on_input, quant_type_id, m, 2 * n, k, True, False,
                               True, is_w1_zp_float)
-    act = torch.empty((m * topk, n), dtype=hidden_states.dtype, device=dev)
-    ops.silu_and_mul(act, c1)
+    if streaming:
+        act = c1     # SiLU-and-mul is applied where the second GEMM reads its rows
+    else:
+        act = torch.empty((m * topk, n), dtype=hidden_states.dtype, device=dev)
+        ops.silu_and_mul(act, c1)
     if topk == 1:
         # one route per row: the second GEMM writes the result itself, there is nothing to sum
         if output is None:
@@ -116,7 +120,7 @@ def fused_marlin_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Te
     ops.moe_wna16_marlin_gemm(act, c3, w2, bias2, w2_scale, None, global_scale2, w2_zeros, None, None,
                               workspace, sorted_ids, expert_ids, num_post, flat_w, block_size_m, 1,
                               not apply_router_weight_on_input, quant_type_id, m * topk, k, n, True, False,
-                              True, is_w2_zp_float)
+                              True, is_w2_zp_float, silu_input=streaming)
     if topk == 1:
         return output
     if output is None:

@@ -532,9 +532,11 @@ def moe_wna16_marlin_gemm(input: torch.Tensor, output: torch.Tensor | None, b_qw
                           b_q_type: ScalarType | int, size_m: int, size_n: int, size_k: int,
                           is_k_full: bool = True, use_atomic_add: bool = False,
                           use_fp32_reduce: bool = False, is_zp_float: bool = False, thread_k: int = -1,
-                          thread_n: int = -1, blocks_per_sm: int = -1) -> torch.Tensor:
+                          thread_n: int = -1, blocks_per_sm: int = -1, silu_input: bool = False) -> torch.Tensor:
     """Grouped expert GEMM; rows follow ``sorted_token_ids`` (flat route ids ``t * top_k + j``).
-    Ignored arguments as in the reference (ops.cu:126-132)."""
+    Ignored arguments as in the reference (ops.cu:126-132).  `silu_input` (no counterpart there; expert weights in
+    the streaming layout only): `input` is the [size_m, 2 * size_k] gate | up output of the layer's first GEMM and
+    silu(gate) * up is what gets multiplied, without a separate SiLU-and-mul pass."""
     lib = _lib.load()
     _check_act_order_absent(g_idx, perm)
     _check(a_scales is None, "a_scales can only be used for 8bit activation.")
@@ -547,7 +549,8 @@ def moe_wna16_marlin_gemm(input: torch.Tensor, output: torch.Tensor | None, b_qw
         _check(moe_block_size % 16 == 0 and 16 <= moe_block_size <= 64,
                f"unsupported moe_block_size={moe_block_size}")
     _check(a.size(0) == size_m, f"Shape mismatch: a.size(0) = {a.size(0)}, size_m = {size_m}")
-    _check(a.size(1) == size_k, f"Shape mismatch: a.size(1) = {a.size(1)}, size_k = {size_k}")
+    _check(a.size(1) == (2 * size_k if silu_input else size_k),
+           f"Shape mismatch: a.size(1) = {a.size(1)}, size_k = {size_k}")
     _check(size_k % 16 == 0, f"size_k = {size_k} is not divisible by tile_size = 16")
     _check(b_qweight.dim() == 3, "b_q_weight must be [experts, size_k / 16, size_n * 16 / pack_factor]")
     num_experts = b_qweight.size(0)
@@ -626,6 +629,10 @@ def moe_wna16_marlin_gemm(input: torch.Tensor, output: torch.Tensor | None, b_qw
 
         if is_prepared(b_qweight, size_k, size_n):
             fmt |= _lib.FMT_PREPARED     # expert weights converted by prepare_weights (decode-sized blocks only)
+        _check(not silu_input or (fmt & _lib.FMT_PREPARED),
+               "silu_input needs expert weights in the streaming layout")
+        if silu_input:
+            fmt |= _lib.FMT_SILU_INPUT
         nbytes = lib.marlin_b200_moe_gemm_scratch_bytes(num_sorted, size_n, size_k, fmt)
         scratch = _scratch(nbytes, a.device)
         _lib.check(lib.marlin_b200_moe_gemm(

@@ -119,3 +119,33 @@ def test_fused_layer_on_streaming_weights(t):
                                  tw.cuda(), ids.cuda(), w13.type_id, w1_streaming=s13, w2_streaming=s2)
     check(out, mo.moe_reference(hidden, w13.deq, w2.deq, tw, ids, round_dtype=torch.bfloat16))
     assert ops.kernel_status() == 0
+
+
+def test_silu_on_load_equals_the_separate_pass():
+    """The second GEMM with SiLU-and-mul applied where it reads its rows returns the bits of the separate
+    SiLU-and-mul pass followed by the same GEMM."""
+    ops, fm = _ops(), _fm()
+    t, e, inter, H = 24, 8, 256, 512
+    g = torch.Generator().manual_seed(40)
+    ids = torch.randint(0, e, (t, 1), generator=g, dtype=torch.int32)
+    tw = torch.rand(t, 1, generator=g)
+    c1 = torch.randn(t, 2 * inter, generator=g).to(torch.bfloat16).cuda()
+    qw = util.make_experts(e, inter, H, "u4b8", torch.bfloat16, seed=41)
+    d = util.to_dev(qw)
+    prepared = ops.prepare_weights(d.packed, inter, H, 4)
+    s, x, npp = fm.moe_align_block_size(ids.cuda(), 16, e, None)
+    ws = torch.empty(0, dtype=torch.int32, device="cuda")
+
+    def gemm(a, silu):
+        c = torch.zeros((t, H), dtype=torch.bfloat16, device="cuda")
+        return ops.moe_wna16_marlin_gemm(a, c, prepared, None, d.scales, None, None, None, None, None, ws, s, x, npp,
+                                         tw.reshape(-1).cuda(), 16, 1, True, qw.type_id, t, H, inter, True, False,
+                                         True, False, silu_input=silu)
+
+    act = torch.empty((t, inter), dtype=torch.bfloat16, device="cuda")
+    ops.silu_and_mul(act, c1)
+    assert torch.equal(gemm(c1, True), gemm(act, False))
+    with pytest.raises(RuntimeError, match="streaming layout"):
+        ops.moe_wna16_marlin_gemm(c1, None, d.packed, None, d.scales, None, None, None, None, None, ws, s, x, npp,
+                                  tw.reshape(-1).cuda(), 16, 1, True, qw.type_id, t, H, inter, True, False, True,
+                                  False, silu_input=True)
