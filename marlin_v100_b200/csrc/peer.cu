@@ -305,7 +305,21 @@ __global__ void __launch_bounds__(512) ep_dispatch_kernel(PeerTable tab, int ran
       }
       const uint4* src = hidden + (int64_t)(route / top_k) * vec_per_row;
       uint4* dst = reinterpret_cast<uint4*>(tab.base[d] + lay.rows) + pos * vec_per_row;
-      for (int v = lane; v < vec_per_row; v += 32) dst[v] = src[v];
+      // all loads of a batch are issued before its first store: a row costs one trip to memory, not one per
+      // 512 bytes (rows of up to 8 KiB in one batch)
+      for (int v0 = 0; v0 < vec_per_row; v0 += 32 * 16) {
+        uint4 buf[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const int v = v0 + u * 32 + lane;
+          if (v < vec_per_row) buf[u] = src[v];
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const int v = v0 + u * 32 + lane;
+          if (v < vec_per_row) dst[v] = buf[u];
+        }
+      }
       if (lane == 0) {
         reinterpret_cast<int32_t*>(tab.base[d] + lay.expert)[pos] = slot_sorted[i] % experts_per_rank;
         reinterpret_cast<float*>(tab.base[d] + lay.weight)[pos] = topk_weights[route];
@@ -359,11 +373,21 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(PeerTable tab, int rank
       __syncthreads();
       for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
         float acc[8] = {};
-        for (int j = 0; j < top_k; ++j) {
-          const uint4 x4 = ld_cg(s_row[j] + v);
-          const T* xp = reinterpret_cast<const T*>(&x4);
+        // the loads of up to eight routes are in flight together (peer loads cost microseconds each); the adds
+        // keep the route order
+        for (int j0 = 0; j0 < top_k; j0 += 8) {
+          uint4 x4[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] += to_float<T>(xp[e]);
+          for (int u = 0; u < 8; ++u)
+            if (j0 + u < top_k) x4[u] = ld_cg(s_row[j0 + u] + v);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            if (j0 + u < top_k) {
+              const T* xp = reinterpret_cast<const T*>(&x4[u]);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[e] += to_float<T>(xp[e]);
+            }
+          }
         }
         uint4 o4;
         T* op = reinterpret_cast<T*>(&o4);
