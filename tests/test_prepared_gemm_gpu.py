@@ -44,3 +44,32 @@ def test_host_pipelined_gemm_matches_operator_call():
         ref = ops.marlin_gemm(x.cuda(), None, d.packed, None, d.scales, None, None, None, None, None, ws,
                               qw.type_id, 16, 512, 512)
         assert torch.equal(y, ref.cpu())
+
+
+def test_host_pipeline_captured_in_a_graph():
+    """The same pipelined calls captured once and replayed: every replay copies the activations in and the
+    results out again, so a changed host buffer shows in the next replay."""
+    from marlin_v100_b200 import ops
+    a, qw = util.make_dense(16, 512, 512, "u4b8", torch.float16, 128)
+    d = util.to_dev(qw)
+    prepared = ops.prepare_weights(d.packed, 512, 512, 4)
+    ws = torch.empty(0, dtype=torch.int32, device="cuda")
+    layers = [dict(packed=d.packed, scales=d.scales), dict(packed=prepared, scales=d.scales)]
+    pipe = ops.HostPipelinedGemm(layers, qw.type_id, 16, 512, 512, torch.float16,
+                                 torch.device("cuda", torch.cuda.current_device()), depth=3)
+    x = torch.randn(16, 512, generator=torch.Generator().manual_seed(3)).to(torch.float16).pin_memory()
+    y = torch.empty(16, 512, dtype=torch.float16).pin_memory()
+    graph = pipe.capture(x, y, [0, 1, 0, 1, 0])          # five calls, the last one on layer 0
+    for scale in (1.0, 0.5):
+        x.mul_(scale)
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = ops.marlin_gemm(x.cuda(), None, d.packed, None, d.scales, None, None, None, None, None, ws,
+                              qw.type_id, 16, 512, 512)
+        assert torch.equal(y, ref.cpu())
+    # the eager form still works afterwards
+    pipe.submit(x, y, layer=1)
+    pipe.synchronize()
+    ref = ops.marlin_gemm(x.cuda(), None, prepared, None, d.scales, None, None, None, None, None, ws, qw.type_id,
+                          16, 512, 512)
+    assert torch.equal(y, ref.cpu())
