@@ -43,6 +43,14 @@
 // chunk's MMAs and epilogue are done.
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag, the kernel drains, frees its tensor
 // memory and reports through g_si8_status.
+//
+// Grouped (expert) form, GROUPED = true (reference operator: csrc/moe/marlin_moe_wna16/ops.cu:102): the same kernel
+// where a "column group" is (block of 8 / 16 routes of the sorted route list, 256 columns of the block's expert).
+// The digit kernel writes the planes in sorted order (row r = activation row sorted_ids[r] / top_k, optionally
+// SiLU-and-mul of a [rows, 2 K] gate | up tensor on the way), the weight producer offsets its stream by the
+// block's expert, scale rows are the expert's, and the epilogue / reduce warps scatter rows to C[sorted_id] with the
+// top-k weight and the expert's bias.  The number of blocks is read from num_tokens_post_pad on the device, after
+// the kernels in front have completed; min(units, launched CTAs) CTAs take part.
 
 #include "codes.cuh"
 #include "common.cuh"
@@ -108,7 +116,6 @@ struct I8Params {
   int cps;                  // chunks per scale row
   int kc, ng;
   int num_ctas;
-  int split;
   uint32_t tx_bytes;        // bytes of the small operands of a chunk
   // grouped (expert) form: a "column group" is (block of NTOK sorted routes, 256 columns of the block's expert)
   const int32_t* sorted_ids;    // [row_capacity] route ids in expert order, >= num_routes for padding
@@ -351,13 +358,8 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_ctas = (int)((U < p.num_ctas) ? (U > 0 ? U : 1) : p.num_ctas);
   int64_t u0 = 0, u1 = 0;
   if ((int)blockIdx.x < num_ctas) {
-    if (p.split) {
-      u0 = range_start(blockIdx.x, U, num_ctas);
-      u1 = range_start(blockIdx.x + 1, U, num_ctas);
-    } else {
-      u0 = range_start(blockIdx.x, ng_total, num_ctas) * p.kc;
-      u1 = range_start(blockIdx.x + 1, ng_total, num_ctas) * p.kc;
-    }
+    u0 = range_start(blockIdx.x, U, num_ctas);
+    u1 = range_start(blockIdx.x + 1, U, num_ctas);
   }
   const int total = (int)(u1 - u0);
   if (tid == 0) {
@@ -789,7 +791,6 @@ int launch_one(const GemmArgs& g) {
   float* chunk_sums = row_scale + 64;
   p.row_scale = row_scale;
   p.chunk_sums = chunk_sums;
-  p.split = 1;
   p.num_ctas = (int)(U < sm_count() ? U : sm_count());
   p.tx_bytes = C::ACT_BYTES + NTOK * 4 + kGroupN * 2 * (format_has_zp(FMT) ? 2 : 1);   // small operands of a chunk
 
@@ -886,7 +887,6 @@ int launch_grouped(const GemmArgs& g) {
   float* chunk_sums = row_scale + ((R + 63) & ~(int64_t)63);
   p.row_scale = row_scale;
   p.chunk_sums = chunk_sums;
-  p.split = 1;
   p.num_ctas = sm_count();
   p.tx_bytes = C::ACT_BYTES + NTOK * 4 + kGroupN * 2 * (format_has_zp(FMT) ? 2 : 1);
 
