@@ -42,3 +42,42 @@ def test_workload_tables_and_selector_names():
     assert b.metric_name("dense_u4_g128_bf16_m4096") == b.METRIC_COMPUTE
     for name, cfg in b.MOE_WORKLOADS.items():
         assert cfg[2] % 8 == 0 and cfg[7] >= 1, name
+
+
+def test_records_of_the_default_line_and_their_data():
+    b = _bench()
+    for name in b.ALSO_WORKLOADS + (b.EP_WORKLOAD,):
+        assert name in b.WORKLOADS or name in b.MOE_WORKLOADS
+    # the streaming layout changes the dominant kernel of the decode sizes, and the traffic figure follows it
+    assert b.dominant_kernel("dense_u4_g128_bf16_m16", 16, 8192, 28672, "streaming") == "stream_i8_kernel"
+    assert b.dominant_kernel("dense_u8b128_ch_bf16_m16", 16, 8192, 28672, "streaming") == "stream_gemm_kernel"
+    traffic = b.ncu_traffic("dense_u4_g128_bf16_m16", "stream_i8_kernel")
+    assert traffic is not None and 1.0 <= traffic / b.algorithmic_bytes("u4", 8192, 28672, 128) <= 1.05
+    assert b.ncu_traffic("dense_u4_g128_bf16_m16", "decode_tc_kernel") is None     # figure of another kernel
+    assert b.ncu_traffic("no_such_workload", "stream_i8_kernel") is None
+    from oracle import marlin_oracle as mo
+    assert b.type_id_of("u4b8") == mo.TYPE_U4B8 and b.type_id_of("mxfp4") == mo.TYPE_FE2M1
+    assert b.type_id_of("fp8") == mo.TYPE_FE4M3 and b.type_id_of("u8") == mo.TYPE_U8
+
+
+def test_expert_placement_of_the_benchmark_router():
+    """The placement the expert-parallel record uses: the busiest rank stays within 1.1x of the mean at 2, 4
+    and 8 ranks on the benchmark's Zipf router (contiguous shards: up to 2.2x)."""
+    import torch
+    from marlin_v100_b200 import parallel
+    b = _bench()
+    fmt, dtype, e, topk, hidden, inter, group, tokens, zipf = b.MOE_WORKLOADS[b.EP_WORKLOAD]
+    g = torch.Generator().manual_seed(3)
+    torch.randn(tokens, hidden, generator=g)
+    logits = torch.randn(tokens, e, generator=g)
+    ranks = torch.randperm(e, generator=g).float() + 1.0
+    pe = ranks.pow(-1.1)
+    logits = logits + (pe / pe.sum()).log()
+    cal = torch.randn(4096, e, generator=torch.Generator().manual_seed(4)) + (pe / pe.sum()).log()
+    expected = torch.bincount(torch.topk(cal, topk, dim=-1).indices.reshape(-1), minlength=e).float()
+    count = torch.bincount(torch.topk(logits, topk, dim=-1).indices.reshape(-1), minlength=e).float()
+    for world in (2, 4, 8):
+        slot = parallel.balanced_expert_placement(expected, world)
+        load = torch.zeros(world)
+        load.index_add_(0, torch.div(slot.long(), e // world, rounding_mode="floor"), count)
+        assert float(load.max() / load.mean()) <= 1.1
