@@ -632,8 +632,12 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (rt == 0) {
         int last = 0;
         if (s_abort == 0) {
-          __threadfence();
-          last = (atomicAdd(p.counters + g, 1) == (int)(pb - pa)) ? 1 : 0;
+          // One release-acquire atomic instead of fence, atomic, fence: the release is cumulative over the epilogue
+          // warps' stores (ordered before this thread by part_ready), the acquire covers the other owners' stores
+          // for every thread behind the barrier below.
+          int old;
+          asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + g) : "memory");
+          last = (old == (int)(pb - pa)) ? 1 : 0;
         }
         s_last = last;
       }
@@ -641,7 +645,6 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int last = s_last;
       reduce_barrier();
       if (!last) continue;
-      __threadfence();
       constexpr int64_t SLOT = NTOK * kGroupN;
       // the first owner holds the group's first chunks (slot 1), every other one a run from midway (slot 0)
       const float4* first = reinterpret_cast<const float4*>(p.partials + (pa * 2 + 1) * SLOT);
