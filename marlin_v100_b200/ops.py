@@ -367,16 +367,23 @@ class HostPipelinedGemm:
     the GEMM of its neighbours; nothing synchronises with the host until `synchronize()`.
 
     `layers` is a list of weight sets, each a dict with `packed`, `scales` and optionally `zeros`,
-    `global_scale`, `bias`; `submit(..., layer=i)` picks one."""
+    `global_scale`, `bias`; `submit(..., layer=i)` picks one.
+
+    `post(c_slot, out_slot)` with `post_shape`: a step that runs behind every GEMM on the compute stream and whose
+    output (a per-slot tensor of `post_shape`) is what gets copied to the host instead of the GEMM's own output,
+    e.g. the all-gather of a column-parallel layer."""
 
     def __init__(self, layers, b_q_type, size_m: int, size_n: int, size_k: int, dtype: torch.dtype,
-                 device: torch.device, depth: int = 3):
+                 device: torch.device, depth: int = 3, post=None, post_shape=None):
         self.depth, self._count = depth, 0
         self.device = device
+        self._post = post
         with torch.cuda.device(device):
             self._in, self._run, self._out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
             self._a = [torch.empty((size_m, size_k), dtype=dtype, device=device) for _ in range(depth)]
             self._c = [torch.empty((size_m, size_n), dtype=dtype, device=device) for _ in range(depth)]
+            self._g = ([torch.empty(tuple(post_shape), dtype=dtype, device=device) for _ in range(depth)]
+                       if post is not None else self._c)
             self._plans = [[PreparedGemm(self._a[s], self._c[s], w["packed"], w.get("bias"), w["scales"],
                                          w.get("global_scale"), w.get("zeros"), b_q_type, size_m, size_n, size_k,
                                          w.get("zeros") is not None) for w in layers] for s in range(depth)]
@@ -403,10 +410,13 @@ class HostPipelinedGemm:
         if reused:
             self._run.wait_event(self._out_done[s])  # this slot's previous result has left the device
         self._plans[s][layer](self._run.cuda_stream)
+        if self._post is not None:
+            with torch.cuda.stream(self._run):
+                self._post(self._c[s], self._g[s])
         self._run_done[s].record(self._run)
         self._out.wait_event(self._run_done[s])
         with torch.cuda.stream(self._out):
-            c_host.copy_(self._c[s], non_blocking=True)
+            c_host.copy_(self._g[s], non_blocking=True)
         self._out_done[s].record(self._out)
 
     def capture(self, a_host: torch.Tensor, c_host: torch.Tensor, layers: list[int]) -> torch.cuda.CUDAGraph:

@@ -155,12 +155,13 @@ class ColumnParallelMarlinLinear:
             self._local = torch.empty((max_m, per), dtype=dtype, device=self.arena.device)
             self._out = torch.empty((max_m, n_total), dtype=dtype, device=self.arena.device)
 
-    def gather(self, local: torch.Tensor) -> torch.Tensor:
-        """Peer-memory all-gather of this rank's [M, N/world] block (contiguous, M <= max_m) into the layer's
-        [M, N] output buffer: one kernel, no host synchronisation."""
+    def gather(self, local: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Peer-memory all-gather of this rank's [M, N/world] block (contiguous, M <= max_m) into `out` [M, N]
+        (default: the layer's own output buffer): one kernel, no host synchronisation."""
         from . import _lib
         m, per = local.shape
-        a, out = self.arena, self._out[:m]
+        a = self.arena
+        out = self._out[:m] if out is None else out
         _lib.check(a._lib.marlin_b200_peer_allgather(a.table, self.rank, self.world, local.data_ptr(),
                                                      m * per * local.element_size(), 4096, out.data_ptr(), m,
                                                      torch.cuda.current_stream(a.device).cuda_stream))
