@@ -42,7 +42,7 @@ extern "C" {
 
 /* Flag, or-ed into the `format` argument of marlin_b200_gemm / marlin_b200_moe_gemm and their scratch-size
  * functions: b_q_weight is in the library's streaming layout (made by marlin_b200_prepare_weights), not in the
- * reference layout.  The grouped GEMM serves such weights for uint4 / uint4b8 with moe_block_size 8 or 16 (the
+ * reference layout.  The grouped GEMM serves such weights for uint4 / uint4b8 with moe_block_size 8, 16 or 32 (the
  * decode regime); marlin_b200_moe_gemm_scratch_bytes then returns the room for digit planes in sorted order. */
 #define MARLIN_B200_FMT_PREPARED 0x100
 /* Flag for marlin_b200_moe_gemm together with MARLIN_B200_FMT_PREPARED: `a` is the [size_m, 2 * size_k]

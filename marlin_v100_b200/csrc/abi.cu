@@ -169,7 +169,7 @@ extern "C" int64_t marlin_b200_gemm_scratch_bytes(int64_t size_m, int64_t size_n
   if (format & MARLIN_B200_FMT_PREPARED) {
     const int64_t a = gemm_stream_scratch_bytes(size_m, size_n, size_k);
     const int f = format & ~MARLIN_B200_FMT_PREPARED;
-    const int64_t b = (size_m <= 16 && (f == kU4B8 || f == kU4)) ? gemm_stream_i8_scratch_bytes(size_m, size_n, size_k) : 0;
+    const int64_t b = (size_m <= 32 && (f == kU4B8 || f == kU4)) ? gemm_stream_i8_scratch_bytes(size_m, size_n, size_k) : 0;
     return a > b ? a : b;
   }
   const int64_t a = gemm_decode_scratch_bytes(size_m, size_n, size_k, format);
@@ -243,7 +243,7 @@ extern "C" int marlin_b200_moe_gemm(const void* a, void* c, const int32_t* b_q_w
   if (g.prepared) {
     // expert weights in the streaming layout: served by the decode-sized integer-MMA kernel only
     MB_CHECK(gemm_stream_i8_grouped_accepts(g),
-             "expert weights in the streaming layout are served for uint4 / uint4b8, moe_block_size 8 or 16, "
+             "expert weights in the streaming layout are served for uint4 / uint4b8, moe_block_size 8, 16 or 32, "
              "size_k %% 128 == 0, size_n %% 256 == 0, group size a multiple of 128 (or per channel) and a scratch "
              "buffer of marlin_b200_moe_gemm_scratch_bytes; pass the reference layout otherwise");
     return launch_gemm_stream_i8_grouped(g);

@@ -170,8 +170,8 @@ int launch_gemm_tc(const GemmArgs& g);              // returns 1 if the shape is
 int launch_gemm_stream_f16(const GemmArgs& g);      // weights in the streaming layout
 int launch_gemm_stream_bf16(const GemmArgs& g);
 int64_t gemm_stream_scratch_bytes(int64_t m, int64_t n, int64_t k);
-bool gemm_stream_i8_accepts(const GemmArgs& g);     // integer-MMA kernel for M <= 16, 4-bit integer formats
-bool gemm_stream_i8_grouped_accepts(const GemmArgs& g);   // its grouped (expert) form: blocks of 8 / 16 routes
+bool gemm_stream_i8_accepts(const GemmArgs& g);     // integer-MMA kernel for M <= 32, 4-bit integer formats
+bool gemm_stream_i8_grouped_accepts(const GemmArgs& g);   // its grouped (expert) form: blocks of 8 / 16 / 32 routes
 int launch_gemm_stream_i8_grouped(const GemmArgs& g);
 int64_t gemm_stream_i8_grouped_scratch_bytes(int64_t num_sorted, int64_t n, int64_t k);
 int launch_gemm_stream_i8(const GemmArgs& g);

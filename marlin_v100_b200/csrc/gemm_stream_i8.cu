@@ -1,4 +1,4 @@
-// Decode-sized GEMM (M <= 16 rows) for 4-bit integer weights in the streaming layout (stream_layout.cuh):
+// Decode-sized GEMM (M <= 32 rows) for 4-bit integer weights in the streaming layout (stream_layout.cuh):
 // integer MMAs on 8-bit operands, weights as the tensor-memory operand.
 //
 //   C[M, N] = A[M, K] * dequant(Wq)[K, N] (+ bias)      (reference operator: csrc/quantization/marlin/marlin.cu:83)
@@ -9,7 +9,7 @@
 // with 16-bit operands it takes 16 MMAs and fifteen instructions per word.
 //
 // The contraction runs transposed, D[n, m] = sum_k W[k, n] * A[m, k]: the 128 rows of an MMA are 128 weight
-// columns, its N = 32 are two digit planes of 16 token columns, accumulation is exact (s32).
+// columns, its N = 16 / 32 / 64 are two digit planes of 8 / 16 / 32 token columns, accumulation is exact (s32).
 //  * Weights.  A word of the streaming layout holds the codes of two columns (8 apart) at four k, one column
 //    in the low nibbles, the other in the high nibbles of its bytes.  `w & 0x0f0f0f0f` is the first column's
 //    byte quadruple (byte = q); `(w ^ 0x80808080) & 0xf0f0f0f0` the second one's (byte = 16 (q - 8) as a signed
@@ -35,7 +35,7 @@
 // producer | 17 and 19 MMA issuers (one 128-column tile each, on two different SM partitions: issuing is what
 // an MMA of this size costs; 17 owns the tensor memory) | 18 producer of the small per-chunk operands (digit
 // tile, digit sums, scale and zero rows) | 20-23 cross-CTA sums of the column groups shared with other CTAs.
-// Four operand stages and four (up to 16 rows) or eight (up to 8 rows) accumulator buffers in tensor memory: the
+// Four operand stages and eight (up to 8 rows), four (up to 16) or two (up to 32) accumulator buffers in tensor memory: the
 // round trip MMA -> epilogue -> next MMA on the same buffer (about 1500 cycles) bounds the rate at one chunk per
 // round trip / buffers.
 // A stage's 16 KiB of packed weights are released as soon as the dequant warps have read them and refilled at
@@ -45,7 +45,7 @@
 // memory and reports through g_si8_status.
 //
 // Grouped (expert) form, GROUPED = true (reference operator: csrc/moe/marlin_moe_wna16/ops.cu:102): the same kernel
-// where a "column group" is (block of 8 / 16 routes of the sorted route list, 256 columns of the block's expert).
+// where a "column group" is (block of 8 / 16 / 32 routes of the sorted route list, 256 columns of the block's expert).
 // The digit kernel writes the planes in sorted order (row r = activation row sorted_ids[r] / top_k, optionally
 // SiLU-and-mul of a [rows, 2 K] gate | up tensor on the way), the weight producer offsets its stream by the
 // block's expert, scale rows are the expert's, and the epilogue / reduce warps scatter rows to C[sorted_id] with the
@@ -75,7 +75,9 @@ constexpr int DCOL = TSTAGES * A_COLS;
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_BARS_FIXED = 5 * STAGES + TSTAGES + 2;
 
-// TOKH = 1: up to 8 token rows, TOKH = 2: up to 16.  An epilogue thread owns one weight column and all token
+// TOKH = 1: up to 8 token rows, TOKH = 2: up to 16, TOKH = 4: up to 32 (one pass over the weights for 17-32 rows:
+// the MMAs take 64 token columns, the epilogue works through the rows eight at a time, two accumulator buffers).
+// An epilogue thread owns one weight column and all token
 // rows (twice the epilogue warps with 8 rows each were measured slower for 16 rows: 51 against 47 us, the
 // register budget of 28 warps makes the epilogue spill).
 template <int TOKH>
@@ -93,9 +95,9 @@ struct Cfg {
   static constexpr int OFF_S = OFF_ACT + ACT_BYTES;
   static constexpr int OFF_Z = OFF_S + kGroupN * 2;
   static constexpr int OFF_SA = OFF_Z + kGroupN * 2;       // NTOK floats
-  static constexpr int STAGE_BYTES = (OFF_SA + 64 + 1023) / 1024 * 1024;
+  static constexpr int STAGE_BYTES = (OFF_SA + (NTOK * 4 > 64 ? NTOK * 4 : 64) + 1023) / 1024 * 1024;
   static constexpr int DBUF_COLS = 2 * NCOL;               // two tiles
-  static constexpr int DBUFS = 256 / DBUF_COLS;            // 8 or 4 accumulator buffers
+  static constexpr int DBUFS = 256 / DBUF_COLS;            // 8, 4 or 2 accumulator buffers
   static constexpr int NUM_BARS = NUM_BARS_FIXED + DBUFS;
   static constexpr int SMEM = 1024 + STAGES * STAGE_BYTES + NUM_BARS * 8 + 64;
   static_assert(DCOL + DBUFS * DBUF_COLS <= TMEM_COLS, "tensor memory budget");
@@ -527,6 +529,34 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if constexpr (format_has_zp(FMT)) zv = to_float<T>(lds_as<T>(st + OFF_Z + nl * 2));
       }
       if (ok && !mbar_wait_park(mma_done(s), ph, &s_abort, 2000)) { atomicExch(&g_si8_status, 6); ok = false; }
+      if constexpr (NTOK == 32) {
+        // eight rows at a time: load both digit planes of the eight, fold them into the running sums, next eight
+        const float t0 = sv * inv_alpha * (1.f / 256.f);
+        const float cfix = sv * beta_minus_zero - zv;
+        if (ok) {
+          tc_fence_after();
+          const uint32_t dbase = tmem + ((uint32_t)(32 * quad) << 16) + DCOL + db * DBUF_COLS + tile * NCOL;
+#pragma unroll
+          for (int q8 = 0; q8 < 4; ++q8) {
+            uint32_t va[8], vb[8];
+            tmem_ld8(dbase + 8 * q8, va);
+            tmem_ld8(dbase + NTOK + 8 * q8, vb);
+            tmem_ld_wait();
+            const uint4 sa0 = lds128(st + OFF_SA + q8 * 32), sa1 = lds128(st + OFF_SA + q8 * 32 + 16);
+            const float sa[8] = {__uint_as_float(sa0.x), __uint_as_float(sa0.y), __uint_as_float(sa0.z),
+                                 __uint_as_float(sa0.w), __uint_as_float(sa1.x), __uint_as_float(sa1.y),
+                                 __uint_as_float(sa1.z), __uint_as_float(sa1.w)};
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+              const int vv = (int)va[m] * 256 + (int)vb[m];   // exact: |D1| < 2^22
+              acc[8 * q8 + m] = fmaf(t0, (float)vv, fmaf(cfix, sa[m], acc[8 * q8 + m]));
+            }
+          }
+          tc_fence_before();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(d_free(db));
+      } else {
       int v[NTOK];
       if (ok) {
         tc_fence_after();
@@ -558,6 +588,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           acc[4 * q + 2] = fmaf(t0, (float)v[4 * q + 2], fmaf(cfix, __uint_as_float(sa.z), acc[4 * q + 2]));
           acc[4 * q + 3] = fmaf(t0, (float)v[4 * q + 3], fmaf(cfix, __uint_as_float(sa.w), acc[4 * q + 3]));
         }
+      }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty(s));
@@ -767,7 +798,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // host side
 // ---------------------------------------------------------------------------------------------------
 int64_t counters_bytes(int64_t n) { return ((n / kGroupN) * 4 + 255) & ~(int64_t)255; }
-int64_t partial_bytes() { return (int64_t)sm_count() * 2 * 16 * kGroupN * (int64_t)sizeof(float); }
+int64_t partial_bytes(int rows = 16) { return (int64_t)sm_count() * 2 * rows * kGroupN * (int64_t)sizeof(float); }
 
 template <typename T, int FMT, int TOKH>
 int launch_one(const GemmArgs& g) {
@@ -786,11 +817,11 @@ int launch_one(const GemmArgs& g) {
   const int64_t U = (int64_t)p.ng * p.kc;
   // scratch: counters | partial sums | digit planes | row factors | per-chunk digit sums
   uint8_t* sc = reinterpret_cast<uint8_t*>(g.scratch);
-  const int64_t cb = counters_bytes(N), pb = partial_bytes();
+  const int64_t cb = counters_bytes(N), pb = partial_bytes(NTOK <= 16 ? 16 : 32);
   p.counters = reinterpret_cast<int*>(sc);
   p.partials = reinterpret_cast<float*>(sc + cb);
   int8_t* digits = reinterpret_cast<int8_t*>(sc + cb + pb);
-  float* row_scale = reinterpret_cast<float*>(digits + (int64_t)32 * K);   // room for the 16-row form
+  float* row_scale = reinterpret_cast<float*>(digits + (int64_t)(NTOK <= 16 ? 32 : 64) * K);   // two planes of 16 / 32 rows
   float* chunk_sums = row_scale + 64;
   p.row_scale = row_scale;
   p.chunk_sums = chunk_sums;
@@ -881,7 +912,7 @@ int launch_grouped(const GemmArgs& g) {
   p.row_capacity = (int)R;
   p.sum_stride = (int)((R + 15) & ~(int64_t)15);
   uint8_t* sc = reinterpret_cast<uint8_t*>(g.scratch);
-  const int64_t cb = grouped_counters_bytes(R, N), pb = partial_bytes();
+  const int64_t cb = grouped_counters_bytes(R, N), pb = partial_bytes(32);
   p.counters = reinterpret_cast<int*>(sc);
   p.partials = reinterpret_cast<float*>(sc + cb);
   int8_t* digits = reinterpret_cast<int8_t*>(sc + cb + pb);
@@ -958,8 +989,8 @@ int launch_grouped(const GemmArgs& g) {
 template <typename T>
 int launch_grouped_dtype(const GemmArgs& g) {
   switch (g.format) {
-    case kU4B8: return g.block_size == 8 ? launch_grouped<T, kU4B8, 1>(g) : launch_grouped<T, kU4B8, 2>(g);
-    case kU4: return g.block_size == 8 ? launch_grouped<T, kU4, 1>(g) : launch_grouped<T, kU4, 2>(g);
+    case kU4B8: return g.block_size == 8 ? launch_grouped<T, kU4B8, 1>(g) : g.block_size == 16 ? launch_grouped<T, kU4B8, 2>(g) : launch_grouped<T, kU4B8, 4>(g);
+    case kU4: return g.block_size == 8 ? launch_grouped<T, kU4, 1>(g) : g.block_size == 16 ? launch_grouped<T, kU4, 2>(g) : launch_grouped<T, kU4, 4>(g);
   }
   return 1;
 }
@@ -967,8 +998,8 @@ int launch_grouped_dtype(const GemmArgs& g) {
 template <typename T>
 int launch_dtype(const GemmArgs& g) {
   switch (g.format) {
-    case kU4B8: return g.size_m <= 8 ? launch_one<T, kU4B8, 1>(g) : launch_one<T, kU4B8, 2>(g);
-    case kU4: return g.size_m <= 8 ? launch_one<T, kU4, 1>(g) : launch_one<T, kU4, 2>(g);
+    case kU4B8: return g.size_m <= 8 ? launch_one<T, kU4B8, 1>(g) : g.size_m <= 16 ? launch_one<T, kU4B8, 2>(g) : launch_one<T, kU4B8, 4>(g);
+    case kU4: return g.size_m <= 8 ? launch_one<T, kU4, 1>(g) : g.size_m <= 16 ? launch_one<T, kU4, 2>(g) : launch_one<T, kU4, 4>(g);
   }
   return 1;
 }
@@ -978,29 +1009,30 @@ int launch_dtype(const GemmArgs& g) {
 // counters, partial sums, then the digit planes (32 x K), the 16 row factors and K / 128 x 16 chunk sums
 int64_t gemm_stream_i8_scratch_bytes(int64_t m, int64_t n, int64_t k) {
   if (m <= 0 || !stream::layout_accepts(k, n)) return 0;
-  return counters_bytes(n) + partial_bytes() + 32 * k + 256 + (k / KCH) * 64;
+  const int rows = m <= 16 ? 16 : 32;
+  return counters_bytes(n) + partial_bytes(rows) + 2 * rows * k + 256 + (k / KCH) * rows * 4;
 }
 
 bool gemm_stream_i8_accepts(const GemmArgs& g) {
   if (g.sorted_ids != nullptr || !g.prepared) return false;
   if (g.format != kU4B8 && g.format != kU4) return false;
-  if (g.size_m <= 0 || g.size_m > 16 || !stream::layout_accepts(g.size_k, g.size_n)) return false;
+  if (g.size_m <= 0 || g.size_m > 32 || !stream::layout_accepts(g.size_k, g.size_n)) return false;
   if (g.num_groups > 1 && (g.size_k / g.num_groups) % KCH != 0) return false;
   if (g.global_scale != nullptr) return false;
   return g.scratch != nullptr && g.scratch_bytes >= gemm_stream_i8_scratch_bytes(g.size_m, g.size_n, g.size_k);
 }
 
-// grouped form: expert weights [E][...] in the streaming layout, blocks of 8 or 16 sorted routes
+// grouped form: expert weights [E][...] in the streaming layout, blocks of 8, 16 or 32 sorted routes
 int64_t gemm_stream_i8_grouped_scratch_bytes(int64_t num_sorted, int64_t n, int64_t k) {
   if (num_sorted <= 0 || !stream::layout_accepts(k, n)) return 0;
-  return grouped_counters_bytes(num_sorted, n) + partial_bytes() + ((2 * num_sorted * k + 255) & ~(int64_t)255) +
+  return grouped_counters_bytes(num_sorted, n) + partial_bytes(32) + ((2 * num_sorted * k + 255) & ~(int64_t)255) +
          ((num_sorted + 63) & ~(int64_t)63) * 4 + (k / KCH) * ((num_sorted + 15) & ~(int64_t)15) * 4 + 256;
 }
 
 bool gemm_stream_i8_grouped_accepts(const GemmArgs& g) {
   if (g.sorted_ids == nullptr || !g.prepared) return false;
   if (g.format != kU4B8 && g.format != kU4) return false;
-  if (g.block_size != 8 && g.block_size != 16) return false;
+  if (g.block_size != 8 && g.block_size != 16 && g.block_size != 32) return false;
   if (g.num_sorted < g.block_size || !stream::layout_accepts(g.size_k, g.size_n)) return false;
   if (g.num_groups > 1 && (g.size_k / g.num_groups) % KCH != 0) return false;
   if (g.global_scale != nullptr) return false;

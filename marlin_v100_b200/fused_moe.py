@@ -64,7 +64,7 @@ def fused_marlin_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Te
     """hidden [M, K] -> [M, K].  w1 [E, K/16, 2N*16/pf] (gate|up), w2 [E, N/16, K*16/pf].
 
     `w1_streaming` / `w2_streaming` (no counterpart in the reference): the same expert weights converted once by
-    `ops.prepare_weights`.  When both are given and the routing leaves at most 16 routes per block (the decode
+    `ops.prepare_weights`.  When both are given and the routing leaves at most 32 routes per block (the decode
     regime, where the layer is bound by streaming the weights of the experts that are hit), the two GEMMs run
     on them with the integer-MMA streaming kernel; larger batches use `w1` / `w2` as before."""
     num_bits = 4 if quant_type_id in _BIT4 else 8
@@ -89,7 +89,7 @@ def fused_marlin_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Te
     if workspace is None:
         workspace = torch.empty(0, dtype=torch.int32, device=dev)
 
-    streaming = w1_streaming is not None and w2_streaming is not None and block_size_m <= 16
+    streaming = w1_streaming is not None and w2_streaming is not None and block_size_m <= 32
     if streaming:
         w1, w2 = w1_streaming, w2_streaming
     sorted_ids, expert_ids, num_post = moe_align_block_size(topk_ids, block_size_m, global_num_experts,

@@ -44,7 +44,7 @@ def activations(m: int, dtype) -> torch.Tensor:
 
 @pytest.mark.parametrize("layout", ["packed", "streaming"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("m", [1, 12, 16])
+@pytest.mark.parametrize("m", [1, 12, 16, 29])
 def test_heavy_tail_rows(weights, dtype, m, layout):
     from marlin_v100_b200 import ops
     qw = weights[dtype]

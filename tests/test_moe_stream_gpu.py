@@ -1,5 +1,5 @@
 """Grouped (expert) GEMM on expert weights in the streaming layout: the decode-sized integer-MMA kernel
-(blocks of 8 or 16 sorted routes), through the C ABI, against the oracle and against the kernel on the
+(blocks of 8, 16 or 32 sorted routes), through the C ABI, against the oracle and against the kernel on the
 reference layout.  Tolerance: mean|d| / mean|ref| <= 1e-2 and max|d| <= 5e-2 max|ref|."""
 import pytest
 import torch
@@ -51,7 +51,7 @@ def test_grouped_streaming_formats(fmt, dtype, block):
 
 
 @pytest.mark.parametrize("t,e,k", [(1, 16, 4), (3, 16, 4), (64, 128, 8), (17, 8, 2)])
-@pytest.mark.parametrize("block", [8, 16])
+@pytest.mark.parametrize("block", [8, 16, 32])
 def test_grouped_streaming_tokens_and_experts(t, e, k, block):
     """Few routes per expert, many experts, empty experts; more units than SMs and fewer."""
     K, N = 1024, 768

@@ -1,5 +1,5 @@
 """Seeded random shapes through the integer-MMA streaming kernel, dense and grouped, against the oracle:
-K in multiples of 128 up to 2304, N in multiples of 256 up to 1792, M 1..16, group sizes 128 / 256 / 384 / per
+K in multiples of 128 up to 2304, N in multiples of 256 up to 1792, M 1..32, group sizes 128 / 256 / 384 / per
 channel where they divide K, both 4-bit integer formats, both activation types, bias on and off.  The split of
 the (column group, chunk) units over the SMs changes with every shape (fewer units than SMs, groups owned by one,
 two or many CTAs), which is what this is after.  Tolerance as everywhere: mean|d| / mean|ref| <= 1e-2 and
@@ -22,7 +22,7 @@ def _cases(seed: int, count: int):
         k = 128 * rnd.randint(1, 18)
         n = 256 * rnd.randint(1, 7)
         groups = [g for g in (128, 256, 384, -1) if g == -1 or k % g == 0]
-        out.append((i, rnd.randint(1, 16), k, n, rnd.choice(groups), rnd.choice(["u4b8", "u4"]),
+        out.append((i, rnd.randint(1, 32), k, n, rnd.choice(groups), rnd.choice(["u4b8", "u4"]),
                     rnd.choice([torch.float16, torch.bfloat16]), rnd.random() < 0.4))
     return out
 
@@ -50,8 +50,8 @@ def test_grouped_random_shapes(i, m, k, n, gs, fmt, dtype, with_bias):
     rnd = random.Random(1000 + i)
     e, top_k = rnd.choice([2, 4, 8, 16]), rnd.choice([1, 2, 4])
     top_k = min(top_k, e)
-    t = m * 3                                    # up to 48 tokens
-    block = rnd.choice([8, 16])
+    t = m * 3                                    # up to 96 tokens
+    block = rnd.choice([8, 16, 32])
     g = torch.Generator().manual_seed(500 + i)
     tw, ids, _ = mo.topk_softmax_reference(torch.randn(t, e, generator=g), top_k, True)
     a = torch.randn(t, k, generator=g).to(dtype)

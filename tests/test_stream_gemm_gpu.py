@@ -142,7 +142,7 @@ def test_strided_a_and_preallocated_c():
 
 
 def test_grouped_gemm_takes_the_flag_only_for_decode_blocks():
-    """Expert weights in the streaming layout are served for blocks of 8 / 16 routes (tests/test_moe_stream_gpu.py);
+    """Expert weights in the streaming layout are served for blocks of 8 / 16 / 32 routes (tests/test_moe_stream_gpu.py);
     any other block size is refused with a message that names the reference layout."""
     from marlin_v100_b200 import _lib
     lib = _lib.load()
