@@ -67,13 +67,11 @@ using stream::kGroupN;
 constexpr int KCH = 128;
 constexpr int NDIG = 2;
 constexpr int DQ_WARPS = 8;
-constexpr int STAGES = 8;
 constexpr int TSTAGES = 4;
 constexpr int RAW_BYTES = KCH * kGroupN / 2;          // 16 KiB
 constexpr int A_COLS = 64;                            // per operand stage: 2 tiles x 32 columns (128 k bytes)
 constexpr int DCOL = TSTAGES * A_COLS;
 constexpr int TMEM_COLS = 512;
-constexpr int NUM_BARS_FIXED = 5 * STAGES + TSTAGES + 2;
 
 // TOKH = 1: up to 8 token rows, TOKH = 2: up to 16, TOKH = 4: up to 32 (one pass over the weights for 17-32 rows:
 // the MMAs take 64 token columns, the epilogue works through the rows eight at a time, two accumulator buffers).
@@ -83,6 +81,8 @@ constexpr int NUM_BARS_FIXED = 5 * STAGES + TSTAGES + 2;
 template <int TOKH>
 struct Cfg {
   static constexpr int NTOK = 8 * TOKH;
+  static constexpr int STAGES = TOKH == 1 ? 8 : (TOKH == 2 ? 8 : 8);   // weight stages in flight, as shared memory allows
+  static constexpr int NUM_BARS_FIXED = 5 * STAGES + TSTAGES + 2;
   static constexpr int NCOL = NDIG * NTOK;                 // token columns of an MMA
   static constexpr int EPI_WARPS = 8;
   static constexpr int DQ_WARP0 = EPI_WARPS;
@@ -139,6 +139,11 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void reduce_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// Arrival by one lane of a converged warp without a divergent branch around it.
+__device__ __forceinline__ void mbar_arrive_if(uint32_t bar, bool pred) {
+  asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 st;\n\tsetp.ne.u32 p, %1, 0;\n\t"
+               "@p mbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar), "r"((uint32_t)pred) : "memory");
+}
 __device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ int64_t range_start(int64_t p, int64_t U, int64_t P) { return p * U / P; }
@@ -325,7 +330,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   using C = Cfg<TOKH>;
   constexpr int NTOK = C::NTOK, NCOL = C::NCOL, EPI_WARPS = C::EPI_WARPS, DQ_WARP0 = C::DQ_WARP0,
                 PROD_WARP = C::PROD_WARP, MMA_WARP = C::MMA_WARP, META_WARP = C::META_WARP, MMA_WARP2 = C::MMA_WARP2,
-                REDUCE_WARP = C::REDUCE_WARP,
+                REDUCE_WARP = C::REDUCE_WARP, STAGES = C::STAGES, NUM_BARS_FIXED = C::NUM_BARS_FIXED,
                 STAGE_BYTES = C::STAGE_BYTES, OFF_ACT = C::OFF_ACT, OFF_S = C::OFF_S, OFF_Z = C::OFF_Z,
                 OFF_SA = C::OFF_SA, DBUF_COLS = C::DBUF_COLS, DBUFS = C::DBUFS, NUM_BARS = C::NUM_BARS;
   extern __shared__ uint8_t smem_raw[];
@@ -388,8 +393,8 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (i < STAGES) count = 1;                                        // full
       else if (i < 2 * STAGES) count = EPI_WARPS;                       // empty
       else if (i < 3 * STAGES) count = 2;                               // mma_done
-      else if (i < 3 * STAGES + TSTAGES) count = DQ_WARPS;              // a_ready
-      else if (i < 4 * STAGES + TSTAGES) count = DQ_WARPS;              // raw_free
+      else if (i < 3 * STAGES + TSTAGES) count = DQ_WARPS / 2;          // a_ready
+      else if (i < 4 * STAGES + TSTAGES) count = DQ_WARPS / 2;          // raw_free
       else if (i < 5 * STAGES + TSTAGES) count = 1;                     // fullm
       else count = EPI_WARPS;                                           // part_ready, d_free
       mbar_init(bar0 + 8u * i, count);
@@ -555,7 +560,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tc_fence_before();
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(d_free(db));
+        mbar_arrive_if(d_free(db), lane == 0);
       } else {
       int v[NTOK];
       if (ok) {
@@ -576,7 +581,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       // the accumulator buffer goes back before the arithmetic: the next MMA on it need not wait for that
       __syncwarp();
-      if (lane == 0) mbar_arrive(d_free(db));
+      mbar_arrive_if(d_free(db), lane == 0);
       if (ok) {
         const float t0 = sv * inv_alpha * (1.f / 256.f);
         const float cfix = sv * beta_minus_zero - zv;
@@ -591,7 +596,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(empty(s));
+      mbar_arrive_if(empty(s), lane == 0);
       if (++db == DBUFS) db = 0;
       if (seg_end) {
         const bool whole = (seg_c0 == 0) && (c == p.kc - 1);
@@ -636,7 +641,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         if (!whole) {   // runs 0 and 1: the reduce warp takes it from here
           __syncwarp();
-          if (lane == 0) mbar_arrive(part_ready(r));
+          mbar_arrive_if(part_ready(r), lane == 0);
         }
         first_segment = false;
       }
@@ -735,54 +740,63 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp < DQ_WARP0 + DQ_WARPS) {
     // ---------------- dequant: per 16-lane half, 8 packed words -> 16 byte quadruples -> one store ----------------
-    const int quad = warp & 3, tile = (warp - DQ_WARP0) >> 2;
-    const uint32_t woff = (uint32_t)((tile * 4 + quad) * 2 * 512 + lane * 16);   // half 1 is 512 bytes further on
+    // Two groups of four warps take alternate chunks (a warp converts both 128-column tiles of its lane quarter),
+    // so that one group's wait for its tensor-memory stores overlaps the other group's loads and conversion.
+    const int quad = warp & 3, grp = (warp - DQ_WARP0) >> 2;
+    const uint32_t woff = (uint32_t)(quad * 2 * 512 + lane * 16);   // tile 1 is 4096 bytes, half 1 512 bytes further on
     const uint32_t t_lane = (uint32_t)(32 * quad) << 16;
     bool ok = true;
-    int s = 0, t = 0, ms = 0;
+    int s = grp, t = grp, ms = grp;
     uint32_t ph = 0, mph = 0;
-    for (int i = 0; i < total; ++i) {
+    for (int i = grp; i < total; i += 2) {
       if (ok && !mbar_wait_park(full(s), ph, &s_abort, 2000)) { atomicExch(&g_si8_status, 7); ok = false; }
       const uint32_t st = base + s * STAGE_BYTES;
-      uint4 x[2][2] = {};
+      uint4 x[2][2][2] = {};
       if (ok) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          x[half][0] = lds128(st + woff + half * 512);
-          x[half][1] = lds128(st + RAW_BYTES / 2 + woff + half * 512);
-        }
+        for (int tile = 0; tile < 2; ++tile)
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            x[tile][half][0] = lds128(st + woff + tile * 4096 + half * 512);
+            x[tile][half][1] = lds128(st + RAW_BYTES / 2 + woff + tile * 4096 + half * 512);
+          }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(raw_free(s));
+      mbar_arrive_if(raw_free(s), lane == 0);
       // the operand stage is free once the MMAs of the chunk that used it last have completed
       if (i >= TSTAGES) {
         if (ok && !mbar_wait_park(mma_done(ms), mph, &s_abort, 2000)) { atomicExch(&g_si8_status, 8); ok = false; }
-        if (++ms == STAGES) { ms = 0; mph ^= 1u; }
+        ms += 2;
+        if (ms >= STAGES) { ms -= STAGES; mph ^= 1u; }
       }
       if (ok) {
         tc_fence_after();
         // registers 4 b .. 4 b + 3 of a store: (lane g: columns 2t, 2t + 1 of 32-k block b), (lane g + 8: same)
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const uint32_t w[8] = {x[half][0].x, x[half][0].y, x[half][0].z, x[half][0].w,
-                                 x[half][1].x, x[half][1].y, x[half][1].z, x[half][1].w};
-          uint32_t r[16];
+        for (int tile = 0; tile < 2; ++tile)
 #pragma unroll
-          for (int b = 0; b < 4; ++b) {
-            r[4 * b + 0] = w[2 * b] & 0x0f0f0f0fu;
-            r[4 * b + 1] = w[2 * b + 1] & 0x0f0f0f0fu;
-            r[4 * b + 2] = (w[2 * b] ^ 0x80808080u) & 0xf0f0f0f0u;
-            r[4 * b + 3] = (w[2 * b + 1] ^ 0x80808080u) & 0xf0f0f0f0u;
+          for (int half = 0; half < 2; ++half) {
+            const uint32_t w[8] = {x[tile][half][0].x, x[tile][half][0].y, x[tile][half][0].z, x[tile][half][0].w,
+                                   x[tile][half][1].x, x[tile][half][1].y, x[tile][half][1].z, x[tile][half][1].w};
+            uint32_t r[16];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              r[4 * b + 0] = w[2 * b] & 0x0f0f0f0fu;
+              r[4 * b + 1] = w[2 * b + 1] & 0x0f0f0f0fu;
+              r[4 * b + 2] = (w[2 * b] ^ 0x80808080u) & 0xf0f0f0f0u;
+              r[4 * b + 3] = (w[2 * b + 1] ^ 0x80808080u) & 0xf0f0f0f0u;
+            }
+            tmem_st_16x256b_x4(tmem + t_lane + ((uint32_t)(16 * half) << 16) + t * A_COLS + tile * 32, r);
           }
-          tmem_st_16x256b_x4(tmem + t_lane + ((uint32_t)(16 * half) << 16) + t * A_COLS + tile * 32, r);
-        }
         tmem_st_wait();
         tc_fence_before();
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(a_ready(t));
-      if (++s == STAGES) { s = 0; ph ^= 1u; }
-      if (++t == TSTAGES) t = 0;
+      mbar_arrive_if(a_ready(t), lane == 0);
+      s += 2;
+      if (s >= STAGES) { s -= STAGES; ph ^= 1u; }
+      t += 2;
+      if (t >= TSTAGES) t -= TSTAGES;
     }
   }
 
