@@ -549,15 +549,18 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             uint32_t va[8], vb[8];
             tmem_ld8(dbase + 8 * q8, va);
             tmem_ld8(dbase + NTOK + 8 * q8, vb);
-            tmem_ld_wait();
+            // the digit-sum term does not need the integer sums: it runs while they are on their way
             const uint4 sa0 = lds128(st + OFF_SA + q8 * 32), sa1 = lds128(st + OFF_SA + q8 * 32 + 16);
             const float sa[8] = {__uint_as_float(sa0.x), __uint_as_float(sa0.y), __uint_as_float(sa0.z),
                                  __uint_as_float(sa0.w), __uint_as_float(sa1.x), __uint_as_float(sa1.y),
                                  __uint_as_float(sa1.z), __uint_as_float(sa1.w)};
 #pragma unroll
+            for (int m = 0; m < 8; ++m) acc[8 * q8 + m] = fmaf(cfix, sa[m], acc[8 * q8 + m]);
+            tmem_ld_wait();
+#pragma unroll
             for (int m = 0; m < 8; ++m) {
               const int vv = (int)va[m] * 256 + (int)vb[m];   // exact: |D1| < 2^22
-              acc[8 * q8 + m] = fmaf(t0, (float)vv, fmaf(cfix, sa[m], acc[8 * q8 + m]));
+              acc[8 * q8 + m] = fmaf(t0, (float)vv, acc[8 * q8 + m]);
             }
           }
           tc_fence_before();
@@ -577,6 +580,19 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld16(dbase, va);
           tmem_ld16(dbase + NTOK, vb);
         }
+        // 16 rows: the digit-sum term does not need the integer sums and runs while they are on their way
+        // (-0.2 us per GEMM; with 8 rows the same order measured +0.4 us)
+        const float cfix = sv * beta_minus_zero - zv;
+        if constexpr (NTOK == 16) {
+#pragma unroll
+        for (int q = 0; q < NTOK / 4; ++q) {   // the chunk's digit sums of the token rows (same for every lane)
+          const uint4 sa = lds128(st + OFF_SA + q * 16);
+          acc[4 * q + 0] = fmaf(cfix, __uint_as_float(sa.x), acc[4 * q + 0]);
+          acc[4 * q + 1] = fmaf(cfix, __uint_as_float(sa.y), acc[4 * q + 1]);
+          acc[4 * q + 2] = fmaf(cfix, __uint_as_float(sa.z), acc[4 * q + 2]);
+          acc[4 * q + 3] = fmaf(cfix, __uint_as_float(sa.w), acc[4 * q + 3]);
+        }
+        }
         tmem_ld_wait();
         tc_fence_before();
 #pragma unroll
@@ -587,14 +603,19 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_arrive_if(d_free(db), lane == 0);
       if (ok) {
         const float t0 = sv * inv_alpha * (1.f / 256.f);
-        const float cfix = sv * beta_minus_zero - zv;
+        if constexpr (NTOK == 16) {
 #pragma unroll
-        for (int q = 0; q < NTOK / 4; ++q) {   // the chunk's digit sums of the token rows (same for every lane)
-          const uint4 sa = lds128(st + OFF_SA + q * 16);
-          acc[4 * q + 0] = fmaf(t0, (float)v[4 * q + 0], fmaf(cfix, __uint_as_float(sa.x), acc[4 * q + 0]));
-          acc[4 * q + 1] = fmaf(t0, (float)v[4 * q + 1], fmaf(cfix, __uint_as_float(sa.y), acc[4 * q + 1]));
-          acc[4 * q + 2] = fmaf(t0, (float)v[4 * q + 2], fmaf(cfix, __uint_as_float(sa.z), acc[4 * q + 2]));
-          acc[4 * q + 3] = fmaf(t0, (float)v[4 * q + 3], fmaf(cfix, __uint_as_float(sa.w), acc[4 * q + 3]));
+          for (int m = 0; m < NTOK; ++m) acc[m] = fmaf(t0, (float)v[m], acc[m]);
+        } else {
+          const float cfix = sv * beta_minus_zero - zv;
+#pragma unroll
+          for (int q = 0; q < NTOK / 4; ++q) {
+            const uint4 sa = lds128(st + OFF_SA + q * 16);
+            acc[4 * q + 0] = fmaf(t0, (float)v[4 * q + 0], fmaf(cfix, __uint_as_float(sa.x), acc[4 * q + 0]));
+            acc[4 * q + 1] = fmaf(t0, (float)v[4 * q + 1], fmaf(cfix, __uint_as_float(sa.y), acc[4 * q + 1]));
+            acc[4 * q + 2] = fmaf(t0, (float)v[4 * q + 2], fmaf(cfix, __uint_as_float(sa.z), acc[4 * q + 2]));
+            acc[4 * q + 3] = fmaf(t0, (float)v[4 * q + 3], fmaf(cfix, __uint_as_float(sa.w), acc[4 * q + 3]));
+          }
         }
       }
       }
