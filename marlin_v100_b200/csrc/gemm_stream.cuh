@@ -18,7 +18,8 @@
 // group, no waiting) adds them in CTA order and writes C, so results repeat bit for bit.
 //
 // Warps (704 threads): 0-3 epilogue (one per 32-lane quadrant of tensor memory) | 4-19 dequant (quadrant =
-// warp % 4, (tile, 16-lane half) = (warp - 4) / 4) | 20 TMA producer | 21 MMA issuer, owns the tensor memory.
+// warp % 4, (tile, chunk parity) = (warp - 4) / 4: two groups of eight warps on alternate chunks, a warp converts
+// both 16-lane halves) | 20 TMA producer | 21 MMA issuer, owns the tensor memory.
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag, the kernel drains, frees its
 // tensor memory and reports through g_stream_status.
 #pragma once
@@ -163,7 +164,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   if (tid == 0) {
     s_abort = 0;
     for (int s = 0; s < STAGES; ++s) { mbar_init(full(s), 1); mbar_init(mma_done(s), 1); }
-    for (int t = 0; t < TSTAGES; ++t) mbar_init(a_ready(t), DQ_WARPS);
+    for (int t = 0; t < TSTAGES; ++t) mbar_init(a_ready(t), DQ_WARPS / 2);
     for (int b = 0; b < NBUF; ++b) { mbar_init(d_full(b), 1); mbar_init(d_free(b), EPI_WARPS); }
     fence_barrier_init();
     prefetch_tensormap(&tmA);
@@ -370,56 +371,67 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
   } else if (warp < DQ_WARP0 + DQ_WARPS) {
     // ---------------- dequant: packed words -> T pairs -> tensor memory ----------------
-    const int quad = warp & 3, idx = (warp - DQ_WARP0) >> 2;     // idx = tile * 2 + half
-    const int tile = idx >> 1, half = idx & 1;
-    const int slab = (tile * 4 + quad) * 2 + half;
+    // Two groups of eight warps take alternate chunks (a warp converts both 16-lane halves of its tile and lane
+    // quarter), so that one group's wait for its tensor-memory stores overlaps the other group's loads and arithmetic.
+    const int quad = warp & 3, idx = (warp - DQ_WARP0) >> 2;     // idx = tile * 2 + group
+    const int tile = idx >> 1, grp = idx & 1;
+    const int slab0 = (tile * 4 + quad) * 2;                      // the warp's slabs: slab0 (lanes 0-15 of the store), slab0 + 1
     const int g8 = lane >> 2;
-    const int nl_a = slab * 16 + g8;                              // the thread's two columns: nl_a, nl_a + 8
     // byte offset of the thread's words inside a 64-k block, and of its scale entries inside a scale row
-    const uint32_t woff = (BITS == 4) ? (uint32_t)(slab * 512 + lane * 16) : (uint32_t)(slab * 1024 + lane * 16);
-    uint32_t soff_a, soff_b;
-    if constexpr (FMT == kNVFP4) {
-      soff_a = (uint32_t)nvfp4_scale_col(nl_a);
-      soff_b = (uint32_t)nvfp4_scale_col(nl_a + 8);
-    } else {
-      soff_a = (uint32_t)nl_a * C::SELEM;
-      soff_b = (uint32_t)(nl_a + 8) * C::SELEM;
+    uint32_t woff[2], soff_a[2], soff_b[2];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int slab = slab0 + hf;
+      const int nl_a = slab * 16 + g8;                            // the thread's two columns: nl_a, nl_a + 8
+      woff[hf] = (BITS == 4) ? (uint32_t)(slab * 512 + lane * 16) : (uint32_t)(slab * 1024 + lane * 16);
+      if constexpr (FMT == kNVFP4) {
+        soff_a[hf] = (uint32_t)nvfp4_scale_col(nl_a);
+        soff_b[hf] = (uint32_t)nvfp4_scale_col(nl_a + 8);
+      } else {
+        soff_a[hf] = (uint32_t)nl_a * C::SELEM;
+        soff_b[hf] = (uint32_t)(nl_a + 8) * C::SELEM;
+      }
     }
-    const uint32_t t_lane = (uint32_t)(32 * quad + 16 * half) << 16;
     bool ok = true;
-    int s = 0, t = 0, ms = 0;   // ms: stage of chunk i - TSTAGES, whose MMAs free operand stage t
+    int s = grp % STAGES, t = grp % TSTAGES, ms = (TSTAGES + grp) & 1;   // ms: stage of chunk i - TSTAGES, whose MMAs free operand stage t
     uint32_t ph = 0, mph = 0;
-    for (int i = 0; i < total; ++i) {
+    for (int i = grp; i < total; i += 2) {
       if (ok && !mbar_wait(full(s), ph, &s_abort)) { atomicExch(&g_stream_status, 6); ok = false; }
       const uint32_t st = base + s * C::STAGE_BYTES;
-      uint32_t x[2][BITS == 4 ? 4 : 8];
-      uint32_t sa = 0, sb = 0, za = 0, zb = 0;
+      uint32_t x[2][2][BITS == 4 ? 4 : 8];
+      uint32_t sa[2] = {0, 0}, sb[2] = {0, 0}, za[2] = {0, 0}, zb[2] = {0, 0};
       if (ok) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint4 v = lds128(st + h * (C::RAW_BYTES / 2) + woff);
-          x[h][0] = v.x; x[h][1] = v.y; x[h][2] = v.z; x[h][3] = v.w;
-          if constexpr (BITS == 8) {
-            const uint4 v2 = lds128(st + h * (C::RAW_BYTES / 2) + woff + 512);
-            x[h][4] = v2.x; x[h][5] = v2.y; x[h][6] = v2.z; x[h][7] = v2.w;
+        for (int hf = 0; hf < 2; ++hf) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint4 v = lds128(st + h * (C::RAW_BYTES / 2) + woff[hf]);
+            x[hf][h][0] = v.x; x[hf][h][1] = v.y; x[hf][h][2] = v.z; x[hf][h][3] = v.w;
+            if constexpr (BITS == 8) {
+              const uint4 v2 = lds128(st + h * (C::RAW_BYTES / 2) + woff[hf] + 512);
+              x[hf][h][4] = v2.x; x[hf][h][5] = v2.y; x[hf][h][6] = v2.z; x[hf][h][7] = v2.w;
+            }
           }
-        }
-        if constexpr (SMODE == 0) {
-          sa = pair16<T>(st + C::OFF_S + soff_a);
-          sb = pair16<T>(st + C::OFF_S + soff_b);
-          if constexpr (format_has_zp(FMT)) {
-            za = pair16<T>(st + C::OFF_Z + soff_a) ^ 0x80008000u;   // -zero * scale
-            zb = pair16<T>(st + C::OFF_Z + soff_b) ^ 0x80008000u;
+          if constexpr (SMODE == 0) {
+            sa[hf] = pair16<T>(st + C::OFF_S + soff_a[hf]);
+            sb[hf] = pair16<T>(st + C::OFF_S + soff_b[hf]);
+            if constexpr (format_has_zp(FMT)) {
+              za[hf] = pair16<T>(st + C::OFF_Z + soff_a[hf]) ^ 0x80008000u;   // -zero * scale
+              zb[hf] = pair16<T>(st + C::OFF_Z + soff_b[hf]) ^ 0x80008000u;
+            }
           }
         }
       }
       // the operand stage is free once the MMAs of the chunk that used it last have completed
       if (i >= TSTAGES) {
         if (ok && !mbar_wait(mma_done(ms), mph, &s_abort)) { atomicExch(&g_stream_status, 7); ok = false; }
-        if (++ms == STAGES) { ms = 0; mph ^= 1u; }
+        ms += 2;
+        if (ms >= STAGES) { ms -= STAGES; mph ^= 1u; }
       }
       if (ok) {
         tc_fence_after();
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           uint32_t r[16];
@@ -428,45 +440,48 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             if constexpr (SMODE == 1) {
               const uint32_t row = (uint32_t)((h * 64 + j * 16) >> p.gs_shift) * (kGroupN * C::SELEM);
               if constexpr (format_scale_is_byte(FMT)) {
-                sa = codes::fp4_scale_pair<T, FMT>(lds8(st + C::OFF_S + row + soff_a));
-                sb = codes::fp4_scale_pair<T, FMT>(lds8(st + C::OFF_S + row + soff_b));
+                sa[hf] = codes::fp4_scale_pair<T, FMT>(lds8(st + C::OFF_S + row + soff_a[hf]));
+                sb[hf] = codes::fp4_scale_pair<T, FMT>(lds8(st + C::OFF_S + row + soff_b[hf]));
               } else {
-                sa = pair16<T>(st + C::OFF_S + row + soff_a);
-                sb = pair16<T>(st + C::OFF_S + row + soff_b);
+                sa[hf] = pair16<T>(st + C::OFF_S + row + soff_a[hf]);
+                sb[hf] = pair16<T>(st + C::OFF_S + row + soff_b[hf]);
                 if constexpr (format_has_zp(FMT)) {
-                  za = pair16<T>(st + C::OFF_Z + row + soff_a) ^ 0x80008000u;
-                  zb = pair16<T>(st + C::OFF_Z + row + soff_b) ^ 0x80008000u;
+                  za[hf] = pair16<T>(st + C::OFF_Z + row + soff_a[hf]) ^ 0x80008000u;
+                  zb[hf] = pair16<T>(st + C::OFF_Z + row + soff_b[hf]) ^ 0x80008000u;
                 }
               }
             }
             // registers of the 16-lane x 8-column store: (lane g8: k 0-1, k 2-3), (lane g8 + 8: k 0-1, k 2-3)
             uint32_t va0, va1, vb0, vb1;
             if constexpr (BITS == 4) {
-              const uint32_t z = x[h][j];
+              const uint32_t z = x[hf][h][j];
               va0 = codes::value4<T, FMT>(z, 0); vb0 = codes::value4<T, FMT>(z, 1);
               va1 = codes::value4<T, FMT>(z, 2); vb1 = codes::value4<T, FMT>(z, 3);
             } else {
-              const uint32_t y0 = x[h][(j >> 1) * 4 + (j & 1) * 2], y1 = x[h][(j >> 1) * 4 + (j & 1) * 2 + 1];
+              const uint32_t y0 = x[hf][h][(j >> 1) * 4 + (j & 1) * 2], y1 = x[hf][h][(j >> 1) * 4 + (j & 1) * 2 + 1];
               va0 = codes::value8<T, FMT>(y0, 0); vb0 = codes::value8<T, FMT>(y0, 1);
               va1 = codes::value8<T, FMT>(y1, 0); vb1 = codes::value8<T, FMT>(y1, 1);
             }
             if constexpr (format_has_zp(FMT)) {
-              r[4 * j + 0] = codes::pfma<T>(va0, sa, za); r[4 * j + 1] = codes::pfma<T>(va1, sa, za);
-              r[4 * j + 2] = codes::pfma<T>(vb0, sb, zb); r[4 * j + 3] = codes::pfma<T>(vb1, sb, zb);
+              r[4 * j + 0] = codes::pfma<T>(va0, sa[hf], za[hf]); r[4 * j + 1] = codes::pfma<T>(va1, sa[hf], za[hf]);
+              r[4 * j + 2] = codes::pfma<T>(vb0, sb[hf], zb[hf]); r[4 * j + 3] = codes::pfma<T>(vb1, sb[hf], zb[hf]);
             } else {
-              r[4 * j + 0] = codes::pmul<T>(va0, sa); r[4 * j + 1] = codes::pmul<T>(va1, sa);
-              r[4 * j + 2] = codes::pmul<T>(vb0, sb); r[4 * j + 3] = codes::pmul<T>(vb1, sb);
+              r[4 * j + 0] = codes::pmul<T>(va0, sa[hf]); r[4 * j + 1] = codes::pmul<T>(va1, sa[hf]);
+              r[4 * j + 2] = codes::pmul<T>(vb0, sb[hf]); r[4 * j + 3] = codes::pmul<T>(vb1, sb[hf]);
             }
           }
-          tmem_st_16x256b_x4(tmem + t_lane + t * A_COLS + tile * 64 + h * 32, r);
+          tmem_st_16x256b_x4(tmem + ((uint32_t)(32 * quad + 16 * hf) << 16) + t * A_COLS + tile * 64 + h * 32, r);
         }
-            tmem_st_wait();
+        }
+        tmem_st_wait();
         tc_fence_before();
-        }
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(a_ready(t));
-      if (++s == STAGES) { s = 0; ph ^= 1u; }
-      if (++t == TSTAGES) t = 0;
+      s += 2;
+      if (s >= STAGES) { s -= STAGES; ph ^= 1u; }
+      t += 2;
+      if (t >= TSTAGES) t -= TSTAGES;
     }
   }
 
