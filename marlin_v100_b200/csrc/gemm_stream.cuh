@@ -17,9 +17,9 @@
 // shared by several CTAs leaves fp32 partial sums in scratch; the CTA that finishes last (a counter per column
 // group, no waiting) adds them in CTA order and writes C, so results repeat bit for bit.
 //
-// Warps (704 threads): 0-3 epilogue (one per 32-lane quadrant of tensor memory) | 4-19 dequant (quadrant =
+// Warps (736 threads): 0-3 epilogue (one per 32-lane quadrant of tensor memory) | 4-19 dequant (quadrant =
 // warp % 4, (tile, chunk parity) = (warp - 4) / 4: two groups of eight warps on alternate chunks, a warp converts
-// both 16-lane halves) | 20 TMA producer | 21 MMA issuer, owns the tensor memory.
+// both 16-lane halves) | 20 TMA producer | 21, 22 MMA issuers (one 128-column tile each; 21 owns the tensor memory).
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag, the kernel drains, frees its
 // tensor memory and reports through g_stream_status.
 #pragma once
@@ -36,8 +36,8 @@ namespace stream {
 using codes::kHalf;
 
 constexpr int KCH = 128;   // k per chunk (two 64-k blocks of the streaming layout)
-constexpr int THREADS = 704;
-constexpr int EPI_WARPS = 4, DQ_WARP0 = 4, DQ_WARPS = 16, PROD_WARP = 20, MMA_WARP = 21;
+constexpr int THREADS = 736;
+constexpr int EPI_WARPS = 4, DQ_WARP0 = 4, DQ_WARPS = 16, PROD_WARP = 20, MMA_WARP = 21, MMA_WARP2 = 22;
 constexpr int TMEM_COLS = 512;
 constexpr int A_COLS = 128;  // tensor-memory columns of one operand stage: 2 tiles x 64 (128 k as 16-bit pairs)
 
@@ -163,9 +163,9 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     s_abort = 0;
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full(s), 1); mbar_init(mma_done(s), 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full(s), 1); mbar_init(mma_done(s), 2); }
     for (int t = 0; t < TSTAGES; ++t) mbar_init(a_ready(t), DQ_WARPS / 2);
-    for (int b = 0; b < NBUF; ++b) { mbar_init(d_full(b), 1); mbar_init(d_free(b), EPI_WARPS); }
+    for (int b = 0; b < NBUF; ++b) { mbar_init(d_full(b), 2); mbar_init(d_free(b), EPI_WARPS); }
     fence_barrier_init();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmS);
@@ -212,9 +212,11 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
     }
-  } else if (warp == MMA_WARP) {
-    // ---------------- MMA issuer ----------------
+  } else if (warp == MMA_WARP || warp == MMA_WARP2) {
+    // ---------------- MMA issuers: one 128-column tile each, on two SM partitions ----------------
+    // (a traced run showed the single issuer as the limit: about 80 cycles per MMA, 16 MMAs per chunk)
     if (lane == 0) {
+      const int tile = (warp == MMA_WARP) ? 0 : 1;
       constexpr uint32_t idesc = instr_desc<T, MT>();
       const uint64_t desc0 = kmajor_sw128_desc(base + C::OFF_ACT);
       const uint32_t desc_lo = (uint32_t)desc0, desc_hi = (uint32_t)(desc0 >> 32);
@@ -234,15 +236,12 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const uint32_t a_base = tmem + t * A_COLS;
         const uint32_t d_base = tmem + C::DCOL + b * (2 * MT);
 #pragma unroll
-        for (int tile = 0; tile < 2; ++tile) {
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t lo = dlo + (uint32_t)(((ks >> 2) * C::ACT_HALF + (ks & 3) * 32) >> 4);
-            if (ks == 0)
-              mma_ts(d_base + tile * MT, a_base + tile * 64, lo, desc_hi, idesc, seg_start ? 0u : 1u);
-            else
-              mma_ts_acc(d_base + tile * MT, a_base + tile * 64 + ks * 8, lo, desc_hi, idesc);
-          }
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t lo = dlo + (uint32_t)(((ks >> 2) * C::ACT_HALF + (ks & 3) * 32) >> 4);
+          if (ks == 0)
+            mma_ts(d_base + tile * MT, a_base + tile * 64, lo, desc_hi, idesc, seg_start ? 0u : 1u);
+          else
+            mma_ts_acc(d_base + tile * MT, a_base + tile * 64 + ks * 8, lo, desc_hi, idesc);
         }
         tc_commit(mma_done(s));
         if (seg_end) {
