@@ -226,7 +226,8 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const bool seg_start = (i == 0) || (c == 0);
         const bool seg_end = (i == total - 1) || (c == p.kc - 1);
         if (seg_start && !mbar_wait_sleep(d_free(b), bph ^ 1u, &s_abort, 100)) { atomicExch(&g_stream_status, 2); break; }
-        if (!mbar_wait_sleep(full(s), ph, &s_abort, 40)) { atomicExch(&g_stream_status, 3); break; }
+        // no wait for full(s): the dequant warps waited for it before they arrived at a_ready(t), and the copy of the
+        // activation tile completes on the same barrier (each wait the lone issuing thread runs costs it 200 cycles)
         if (!mbar_wait_sleep(a_ready(t), tph, &s_abort, 20)) { atomicExch(&g_stream_status, 4); break; }
         tc_fence_after();
         // The issuing thread shares its scheduler with four dequant warps, so every instruction it needs
