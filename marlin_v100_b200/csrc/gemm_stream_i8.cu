@@ -426,6 +426,9 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int len = s_run_len[r];
         int g = s_run_g[r], c = s_run_c[r];
         for (int j = 0; j < len; ++j, ++i) {
+          // the ring is filled in two steps: two copies at once, the rest when the first has landed, so that no SM's
+          // first chunk queues behind other SMs' sixth (-0.3 us at 16 rows)
+          if (i == 2 && !mbar_wait_park(full(0), 0, &s_abort, 2000)) { atomicExch(&g_si8_status, 1); ok = false; break; }
           if (i >= STAGES && !mbar_wait_park(raw_free(s), ph ^ 1u, &s_abort, 2000)) { atomicExch(&g_si8_status, 1); ok = false; break; }
           mbar_arrive_expect_tx(full(s), RAW_BYTES);
           if constexpr (GROUPED) {
