@@ -349,10 +349,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       int g = (int)(u0 / p.kc);
       int c = (int)(u0 - (int64_t)g * p.kc) + lane;
       while (c >= p.kc) { c -= p.kc; ++g; }
-      int s = lane;
+      int s = lane, issued = 0;
       uint32_t phase = 0;
       bool first_lap = true;
-      for (int it = lane; it < total; it += PAIRS) {
+      for (int it = lane; it < total; it += PAIRS, ++issued) {
         if (!first_lap) {
           if (!mbar_wait(empty_bar(s), phase ^ 1u, &s_abort)) {
             atomicExch(&g_decode_status, 1);
@@ -373,6 +373,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         s += PAIRS;
         if (s >= STAGES) { s -= STAGES; phase ^= 1u; first_lap = false; }
       }
+      // no copy of this lane's is in flight when it leaves (a CTA must not exit with copies on their way into its
+      // shared memory; after a give-up nobody else waits for them): its stages are lane, lane + PAIRS, ...
+      if (s_abort != 0) drain_copies([&](int idx) { return full_bar(lane + PAIRS * idx); }, STAGES / PAIRS, issued);
     }
     return;
   }

@@ -249,6 +249,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   auto d_free = [&](int b) { return bar0 + 8u * (3 * STAGES + TSTAGES + b); };
   auto sum_full = [&](int b) { return bar0 + 8u * (3 * STAGES + TSTAGES + 2 + b); };
   const uint32_t tmem_slot = bar0 + 8u * NUM_BARS;
+  auto drain_bar = [&](int w) { return bar0 + 8u * NUM_BARS + 16u + 8u * w; };   // give-up path of the MMA issuers
 
   __shared__ int s_abort;
   __shared__ float s_asum[2][16];
@@ -263,6 +264,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
     for (int t = 0; t < TSTAGES; ++t) mbar_init(a_ready(t), DQ_WARPS);
     for (int b = 0; b < 2; ++b) { mbar_init(d_free(b), EPI_WARPS); mbar_init(sum_full(b), 1); }
+    mbar_init(drain_bar(0), 1);
+    mbar_init(drain_bar(1), 1);
     fence_barrier_init();
     prefetch_tensormap(&tmW);
     prefetch_tensormap(&tmA);
@@ -310,8 +313,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       c += 4;
       while (c >= p.kc) { c -= p.kc; ++g; }
       const int g1 = g, c1 = c;
-      if (lane < total) issue(lane, g0, c0, true, false);
-      if (lane + 4 < total) issue(lane + 4, g1, c1, true, false);
+      int last = -1;   // the last chunk this lane has issued copies for
+      if (lane < total) { issue(lane, g0, c0, true, false); last = lane; }
+      if (lane + 4 < total) { issue(lane + 4, g1, c1, true, false); last = lane + 4; }
       pdl_wait_prior_grid();
       if (lane < total) issue(lane, g0, c0, false, true);
       if (lane + 4 < total) issue(lane + 4, g1, c1, false, true);
@@ -324,11 +328,16 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         // (the MMA's B operand) only once the MMAs that read the old one have completed
         if (!mbar_wait(empty(s), ph ^ 1u, &s_abort)) { atomicExch(&g_dtc_status, 1); break; }
         issue(i, g, c, true, false);
+        last = i;
         if (!mbar_wait(mma_done(s), ph ^ 1u, &s_abort)) { atomicExch(&g_dtc_status, 1); break; }
         issue(i, g, c, false, true);
         c += 4;
         while (c >= p.kc) { c -= p.kc; ++g; }
       }
+      // no copy of this lane's is in flight when it leaves (a CTA must not exit with copies on their way into its
+      // shared memory; after a give-up nobody else waits for them)
+      if (s_abort != 0)
+        for (int i = last; i >= 0 && i > last - STAGES; i -= 4) drain_barrier(full(i & (STAGES - 1)), (uint32_t)(i / STAGES) & 1u);
     }
   } else if (warp == 1 || warp == 2) {
     // ---------------- MMA issuers: warp 1 for the first 128-column tile, warp 2 for the second ----------------
@@ -353,6 +362,11 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           tc_mma_i8_ts(d_addr, a_addr + kb * 8, desc + kb * 2, idesc, (sc_start && kb == 0) ? 0u : 1u);
         tc_commit(mma_done(s));
         if (sc_end) ++j;
+      }
+      // the tensor memory is freed only after this thread's MMAs have completed (after a give-up nobody else waits)
+      if (s_abort != 0) {
+        tc_commit(drain_bar(tile));
+        drain_barrier(drain_bar(tile), 0);
       }
     }
   } else if (warp == 3) {

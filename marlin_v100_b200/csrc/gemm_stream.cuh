@@ -157,6 +157,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   auto d_full = [&](int b) { return bar0 + 8u * (2 * STAGES + TSTAGES + b); };
   auto d_free = [&](int b) { return bar0 + 8u * (2 * STAGES + TSTAGES + NBUF + b); };
   const uint32_t tmem_slot = bar0 + 8u * C::NUM_BARS;
+  auto drain_bar = [&](int w) { return bar0 + 8u * C::NUM_BARS + 16u + 8u * w; };   // give-up path of the MMA issuers
 
   __shared__ int s_abort;
   __shared__ int s_last;
@@ -166,6 +167,8 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     for (int s = 0; s < STAGES; ++s) { mbar_init(full(s), 1); mbar_init(mma_done(s), 2); }
     for (int t = 0; t < TSTAGES; ++t) mbar_init(a_ready(t), DQ_WARPS / 2);
     for (int b = 0; b < NBUF; ++b) { mbar_init(d_full(b), 2); mbar_init(d_free(b), EPI_WARPS); }
+    mbar_init(drain_bar(0), 1);
+    mbar_init(drain_bar(1), 1);
     fence_barrier_init();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmS);
@@ -196,9 +199,9 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   if (warp == PROD_WARP) {
     // ---------------- producer: one bulk copy of the chunk's weights, the activation tile, the scale rows --------
     if (lane == 0) {
-      int g = g_first, c = c_first, s = 0;
+      int g = g_first, c = c_first, s = 0, i = 0;
       uint32_t ph = 0;
-      for (int i = 0; i < total; ++i) {
+      for (; i < total; ++i) {
         if (i >= STAGES && !mbar_wait_sleep(mma_done(s), ph ^ 1u, &s_abort, 100)) { atomicExch(&g_stream_status, 1); break; }
         const uint32_t st = base + s * C::STAGE_BYTES;
         mbar_arrive_expect_tx(full(s), p.tx_bytes);
@@ -211,6 +214,9 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (++c == p.kc) { c = 0; ++g; }
         if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
+      // after a give-up nobody waits for the copies this thread issued last, and a CTA must not exit with copies on
+      // their way into its shared memory
+      if (s_abort != 0) drain_copies(full, STAGES, i);
     }
   } else if (warp == MMA_WARP || warp == MMA_WARP2) {
     // ---------------- MMA issuers: one 128-column tile each, on two SM partitions ----------------
@@ -252,6 +258,11 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (++c == p.kc) c = 0;
         if (++s == STAGES) { s = 0; ph ^= 1u; }
         if (++t == TSTAGES) { t = 0; tph ^= 1u; }
+      }
+      // after a give-up nobody waits for this thread's MMAs: the tensor memory is freed only once they have completed
+      if (s_abort != 0) {
+        tc_commit(drain_bar(tile));
+        drain_barrier(drain_bar(tile), 0);
       }
     }
   } else if (warp < EPI_WARPS) {

@@ -348,6 +348,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   auto part_ready = [&](int r) { return bar0 + 8u * (5 * STAGES + TSTAGES + r); };  // a partial sum is in scratch
   auto d_free = [&](int b) { return bar0 + 8u * (NUM_BARS_FIXED + b); };
   const uint32_t tmem_slot = bar0 + 8u * NUM_BARS;
+  auto drain_bar = [&](int w) { return bar0 + 8u * NUM_BARS + 16u + 8u * w; };   // give-up path of the MMA issuers
 
   __shared__ int s_abort;
   __shared__ int s_last;
@@ -402,6 +403,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       else count = EPI_WARPS;                                           // part_ready, d_free
       mbar_init(bar0 + 8u * i, count);
     }
+    if (lane < 2) mbar_init(drain_bar(lane), 1);
     fence_barrier_init();
   }
   if (warp == MMA_WARP) {
@@ -446,6 +448,9 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
       }
+      // after a give-up nobody waits for the copies this thread issued last, and a CTA must not exit with copies on
+      // their way into its shared memory
+      if (s_abort != 0) drain_copies(full, STAGES, i);
     }
   } else if (warp == META_WARP) {
     // ---------------- producer of the digit tile, the digit sums and the scale / zero rows ----------------
@@ -481,6 +486,7 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
       }
+      if (s_abort != 0) drain_copies(fullm, STAGES, i);
     }
   } else if (warp == MMA_WARP || warp == MMA_WARP2) {
     // ---------------- MMA issuers: one 128-column tile each, 4 blocks of 32 k per chunk ----------------
@@ -505,6 +511,11 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (++s == STAGES) { s = 0; ph ^= 1u; }
         if (++t == TSTAGES) { t = 0; tph ^= 1u; }
         if (++b == DBUFS) { b = 0; bph ^= 1u; }
+      }
+      // after a give-up nobody waits for this thread's MMAs: the tensor memory is freed only once they have completed
+      if (s_abort != 0) {
+        tc_commit(drain_bar(tile));
+        drain_barrier(drain_bar(tile), 0);
       }
     }
   } else if (warp < EPI_WARPS) {

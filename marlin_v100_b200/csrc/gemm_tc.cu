@@ -56,7 +56,7 @@ struct TcLayout {
   static constexpr int OFF_B = OFF_A + A_STAGES * A_BYTES;
   static constexpr int OFF_BAR = OFF_B + B_STAGES * B_BYTES;
   static constexpr int NUM_BARS = 2 * RAW_STAGES + 2 * A_STAGES + 2 * B_STAGES + 2;
-  static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16;
+  static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16;   // + tensor-memory slot, + the issuer's drain barrier
 };
 
 struct TcParams {
@@ -309,6 +309,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const uint32_t acc_full = bar0 + 8u * (2 * RS + 2 * AS + 2 * BS);
   const uint32_t acc_empty = acc_full + 8u;
   const uint32_t tmem_slot = acc_empty + 8u;
+  const uint32_t drain_bar = tmem_slot + 8u;   // the MMA issuer's own commit before the tensor memory is freed
 
   __shared__ int s_abort;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -317,6 +318,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     for (int s = 0; s < RS; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DQ_WARPS); }
     for (int s = 0; s < AS; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
     for (int s = 0; s < BS; ++s) { mbar_init(b_full(s), DQ_WARPS); mbar_init(b_empty(s), 1); }
+    mbar_init(drain_bar, 1);
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 4);
     fence_barrier_init();
@@ -342,7 +344,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   if (warp == 0) {
     // ---------------- packed-weight producer ----------------
     if (lane == 0) {
-      int s = 0;
+      int s = 0, issued = 0;
       uint32_t ph = 0;
       bool ok = true;
       TcWalk wk(p);
@@ -358,13 +360,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           tma_load_2d(st + L::RAW_W, &tmS, raw_full(s), nt * BN, srow);
           if constexpr (format_has_zp(FMT)) tma_load_2d(st + L::RAW_W + META, &tmZ, raw_full(s), nt * BN, srow);
           if (++s == RS) { s = 0; ph ^= 1u; }
+          ++issued;
         }
       }
+      if (s_abort != 0) drain_copies(raw_full, RS, issued);   // no copy of this thread's is in flight when it leaves
     }
   } else if (warp == 1) {
     // ---------------- activation producer ----------------
     if (lane == 0) {
-      int s = 0;
+      int s = 0, issued = 0;
       uint32_t ph = 0;
       bool ok = true;
       TcWalk wk(p);
@@ -376,8 +380,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           mbar_arrive_expect_tx(a_full(s), p.a_tx);
           tma_load_2d(base + L::OFF_A + s * L::A_BYTES, &tmA, a_full(s), c * BK, mt * 128 * MT);
           if (++s == AS) { s = 0; ph ^= 1u; }
+          ++issued;
         }
       }
+      if (s_abort != 0) drain_copies(a_full, AS, issued);
     }
   } else if (warp == 2) {
     // ---------------- MMA issuer ----------------
@@ -416,6 +422,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         }
         if (ok) tc_commit(acc_full);
         phacc ^= 1u;
+      }
+      // the tensor memory is freed only after this thread's MMAs have completed (after a give-up nobody else waits)
+      if (s_abort != 0) {
+        tc_commit(drain_bar);
+        drain_barrier(drain_bar, 0);
       }
     }
   } else if (warp >= 4 && warp < 8) {
@@ -755,6 +766,7 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const uint32_t acc_full = bar0 + 8u * (2 * RS + 2 * AS + 2 * BS);
   const uint32_t acc_empty = acc_full + 8u;
   const uint32_t tmem_slot = acc_empty + 8u;
+  const uint32_t drain_bar = tmem_slot + 8u;   // the MMA issuer's own commit before the tensor memory is freed
 
   __shared__ int s_abort;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -763,6 +775,7 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     for (int s = 0; s < RS; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DQ_WARPS); }
     for (int s = 0; s < AS; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
     for (int s = 0; s < BS; ++s) { mbar_init(b_full(s), DQ_WARPS); mbar_init(b_empty(s), 1); }
+    mbar_init(drain_bar, 1);
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 4);
     fence_barrier_init();
@@ -788,7 +801,7 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   if (warp == 0) {
     // ---------------- packed-weight producer ----------------
     if (lane == 0) {
-      int s = 0;
+      int s = 0, issued = 0;
       uint32_t ph = 0;
       bool ok = true;
       while (ok && iter.next(e, row_lo, row_hi)) {
@@ -802,8 +815,10 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           tma_load_2d(st + L::RAW_W, &tmS, raw_full(s), iter.nt * BN, srow);
           if constexpr (format_has_zp(FMT)) tma_load_2d(st + L::RAW_W + META, &tmZ, raw_full(s), iter.nt * BN, srow);
           if (++s == RS) { s = 0; ph ^= 1u; }
+          ++issued;
         }
       }
+      if (s_abort != 0) drain_copies(raw_full, RS, issued);   // no copy of this thread's is in flight when it leaves
     }
   } else if (warp == 1) {
     // ---------------- activation producer ----------------
@@ -813,7 +828,7 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     // number of copies the load/store unit keeps in flight - about 128 cycles per warp instruction -
     // and TMA gather4 loads cost about 100 cycles of issue time per 4 rows; both starve the MMA.)
     if (lane == 0) {
-      int s = 0;
+      int s = 0, issued = 0;
       uint32_t ph = 0;
       bool ok = true;
       while (ok && iter.next(e, row_lo, row_hi)) {
@@ -823,8 +838,10 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           mbar_arrive_expect_tx(a_full(s), L::A_BYTES);
           tma_load_2d(base + L::OFF_A + s * L::A_BYTES, &tmA, a_full(s), c * BK, row0);
           if (++s == AS) { s = 0; ph ^= 1u; }
+          ++issued;
         }
       }
+      if (s_abort != 0) drain_copies(a_full, AS, issued);
     }
   } else if (warp == 2) {
     // ---------------- MMA issuer ----------------
@@ -857,6 +874,11 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         }
         if (ok) tc_commit(acc_full);
         phacc ^= 1u;
+      }
+      // the tensor memory is freed only after this thread's MMAs have completed (after a give-up nobody else waits)
+      if (s_abort != 0) {
+        tc_commit(drain_bar);
+        drain_barrier(drain_bar, 0);
       }
     }
   } else if (warp >= 4 && warp < 8) {

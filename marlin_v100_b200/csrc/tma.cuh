@@ -133,6 +133,32 @@ __device__ __forceinline__ bool mbar_wait_park(uint32_t bar, uint32_t parity, vo
   }
 }
 
+// For the give-up path of a producer thread: a CTA must not exit while copies into its shared memory are in
+// flight.  Waits (bounded by about 50 ms, not by the abort flag, which is set by then) until the copy issued last
+// into every stage of a ring has landed: `issued` copies went to stages 0, 1, ... round robin, and `bar_of(s)` is the
+// barrier a copy into stage s completes on.  In a run without a give-up every copy has been consumed before the
+// kernel ends, and a producer that finished its loop long before a give-up has nothing in flight either (a wait
+// gives up after two seconds), so callers use this when they leave their loop with the abort flag up.
+template <class BarOf>
+__device__ __forceinline__ void drain_copies(BarOf bar_of, int stages, int issued) {
+  const uint64_t t0 = global_timer_ns();
+  for (int j = (issued > stages) ? issued - stages : 0; j < issued; ++j) {
+    const uint32_t bar = bar_of(j % stages), parity = (uint32_t)((j / stages) & 1);
+#pragma unroll 1
+    while (!mbar_try_wait_hint(bar, parity, 1000)) {
+      if (global_timer_ns() - t0 > 50000000ull) return;
+    }
+  }
+}
+// The same for one barrier (an MMA issuer's own tcgen05.commit before the tensor memory is freed).
+__device__ __forceinline__ void drain_barrier(uint32_t bar, uint32_t parity) {
+  const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+  while (!mbar_try_wait_hint(bar, parity, 1000)) {
+    if (global_timer_ns() - t0 > 50000000ull) return;
+  }
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
                                             int c1) {
   asm volatile(
