@@ -296,6 +296,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   using L = TcLayout<BITS, MT>;
   constexpr int RS = L::RAW_STAGES, AS = L::A_STAGES, BS = L::B_STAGES;
   constexpr uint32_t NCOLS = 256 * MT;
+  // With three operand stages the dequant warps work in two groups of eight on alternate chunks (a warp takes both
+  // column halves of its 8-k slice): one group's barrier round trips overlap the other group's conversion.
+  constexpr bool DQ_SPLIT = (BS == 3) && (RS % 2 == 0);
+  constexpr int DQ_ARRIVALS = DQ_SPLIT ? DQ_WARPS / 2 : DQ_WARPS;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -315,9 +319,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     s_abort = 0;
-    for (int s = 0; s < RS; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DQ_WARPS); }
+    for (int s = 0; s < RS; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DQ_ARRIVALS); }
     for (int s = 0; s < AS; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
-    for (int s = 0; s < BS; ++s) { mbar_init(b_full(s), DQ_WARPS); mbar_init(b_empty(s), 1); }
+    for (int s = 0; s < BS; ++s) { mbar_init(b_full(s), DQ_ARRIVALS); mbar_init(b_empty(s), 1); }
     mbar_init(drain_bar, 1);
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 4);
@@ -484,11 +488,39 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   } else if (warp >= 8) {
     // ---------------- dequantisation ----------------
     const int d = warp - 8;
-    int sr = 0, sb = 0;
-    uint32_t phr = 0, phb = 0;
     bool ok = true;
     TcWalk wk(p);
     TcItem it;
+    if constexpr (DQ_SPLIT) {
+      const int grp = d >> 3, d8 = d & 7;
+      int sr = grp % RS, sb = grp % BS, j = 0;
+      uint32_t phr = 0, phb = 0;
+      while (ok && wk.next(p, SLOT_ELEMS, it)) {
+        for (int c = it.c0; c < it.c1; ++c, ++j) {
+          if ((j & 1) != grp) continue;
+          if (!mbar_wait(raw_full(sr), phr, &s_abort) || !mbar_wait(b_empty(sb), phb ^ 1u, &s_abort)) {
+            atomicExch(&g_tc_status, 6);
+            ok = false;
+            break;
+          }
+          const uint32_t raw = base + L::OFF_RAW + sr * L::RAW_BYTES, bt = base + L::OFF_B + sb * L::B_BYTES;
+          dequant_chunk<T, FMT>(raw, bt, d8, lane, p.rpc, p.group_size);
+          dequant_chunk<T, FMT>(raw, bt, d8 + 8, lane, p.rpc, p.group_size);
+          fence_proxy_async();  // the tensor core reads the tile through the async proxy
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(b_full(sb));
+            mbar_arrive(raw_empty(sr));
+          }
+          sr += 2;
+          if (sr >= RS) { sr -= RS; phr ^= 1u; }
+          sb += 2;
+          if (sb >= BS) { sb -= BS; phb ^= 1u; }
+        }
+      }
+    } else {
+    int sr = 0, sb = 0;
+    uint32_t phr = 0, phb = 0;
     while (ok && wk.next(p, SLOT_ELEMS, it)) {
       for (int c = it.c0; c < it.c1; ++c) {
         if (!mbar_wait(raw_full(sr), phr, &s_abort) || !mbar_wait(b_empty(sb), phb ^ 1u, &s_abort)) {
@@ -507,6 +539,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         if (++sr == RS) { sr = 0; phr ^= 1u; }
         if (++sb == BS) { sb = 0; phb ^= 1u; }
       }
+    }
     }
   }
 
