@@ -46,11 +46,12 @@ struct TcLayout {
   // as deep as shared memory allows: with few row tiles the kernel streams weights and the ring
   // depth is what hides the HBM latency
   static constexpr int RAW_STAGES = (AST != 3) ? (BITS == 4 ? (MT == 1 ? 5 : 6) : 4)   // grouped kernel
-                                    : (MT == 1 ? (BITS == 4 ? 6 : 5) : (BITS == 4 ? 5 : 3));
+                                    : (MT == 1 ? (BITS == 4 ? 6 : 4) : (BITS == 4 ? 5 : 3));
   static constexpr int A_BYTES = MT * 128 * 128;
   static constexpr int A_STAGES = AST;
   static constexpr int B_BYTES = BN * 128;
-  static constexpr int B_STAGES = (MT == 1 && BITS == 4) ? 3 : 2;
+  // three operand stages where they fit: the dense kernel then runs its dequant warps in two groups
+  static constexpr int B_STAGES = (MT == 1 && (BITS == 4 || AST == 3)) ? 3 : 2;
   static constexpr int OFF_RAW = 0;
   static constexpr int OFF_A = OFF_RAW + RAW_STAGES * RAW_BYTES;
   static constexpr int OFF_B = OFF_A + A_STAGES * A_BYTES;
