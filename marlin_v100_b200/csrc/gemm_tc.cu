@@ -45,7 +45,7 @@ struct TcLayout {
   static constexpr int RAW_BYTES = RAW_W + 2 * META;
   // as deep as shared memory allows: with few row tiles the kernel streams weights and the ring
   // depth is what hides the HBM latency
-  static constexpr int RAW_STAGES = (AST != 3) ? (BITS == 4 ? (MT == 1 ? 5 : 6) : 4)   // grouped kernel
+  static constexpr int RAW_STAGES = (AST != 3) ? (BITS == 4 ? (MT == 1 ? 4 : 6) : 4)   // grouped kernel
                                     : (MT == 1 ? (BITS == 4 ? 6 : 4) : (BITS == 4 ? 5 : 3));
   static constexpr int A_BYTES = MT * 128 * 128;
   static constexpr int A_STAGES = AST;
@@ -787,6 +787,9 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   using L = TcLayout<BITS, MT, MT == 1 ? MOE_A_STAGES : 3>;
   constexpr int RS = L::RAW_STAGES, AS = L::A_STAGES, BS = L::B_STAGES;
   constexpr uint32_t NCOLS = 256 * MT;
+  // with three operand stages the dequant warps work in two groups of eight on alternate chunks (see tc_gemm_kernel)
+  constexpr bool DQ_SPLIT = (BS == 3) && (RS % 2 == 0);
+  constexpr int DQ_ARRIVALS = DQ_SPLIT ? DQ_WARPS / 2 : DQ_WARPS;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -806,9 +809,9 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     s_abort = 0;
-    for (int s = 0; s < RS; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DQ_WARPS); }
+    for (int s = 0; s < RS; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DQ_ARRIVALS); }
     for (int s = 0; s < AS; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
-    for (int s = 0; s < BS; ++s) { mbar_init(b_full(s), DQ_WARPS); mbar_init(b_empty(s), 1); }
+    for (int s = 0; s < BS; ++s) { mbar_init(b_full(s), DQ_ARRIVALS); mbar_init(b_empty(s), 1); }
     mbar_init(drain_bar, 1);
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 4);
@@ -970,9 +973,37 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   } else if (warp >= 8) {
     // ---------------- dequantisation ----------------
     const int d = warp - 8;
+    bool ok = true;
+    if constexpr (DQ_SPLIT) {
+      const int grp = d >> 3, d8 = d & 7;
+      int sr = grp % RS, sb = grp % BS, j = 0;
+      uint32_t phr = 0, phb = 0;
+      while (ok && iter.next(e, row_lo, row_hi)) {
+        for (int c = 0; c < p.kc; ++c, ++j) {
+          if ((j & 1) != grp) continue;
+          if (!mbar_wait(raw_full(sr), phr, &s_abort) || !mbar_wait(b_empty(sb), phb ^ 1u, &s_abort)) {
+            atomicExch(&g_tc_status, 16);
+            ok = false;
+            break;
+          }
+          const uint32_t raw = base + L::OFF_RAW + sr * L::RAW_BYTES, bt = base + L::OFF_B + sb * L::B_BYTES;
+          dequant_chunk<T, FMT>(raw, bt, d8, lane, p.rpc, p.group_size);
+          dequant_chunk<T, FMT>(raw, bt, d8 + 8, lane, p.rpc, p.group_size);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(b_full(sb));
+            mbar_arrive(raw_empty(sr));
+          }
+          sr += 2;
+          if (sr >= RS) { sr -= RS; phr ^= 1u; }
+          sb += 2;
+          if (sb >= BS) { sb -= BS; phb ^= 1u; }
+        }
+      }
+    } else {
     int sr = 0, sb = 0;
     uint32_t phr = 0, phb = 0;
-    bool ok = true;
     while (ok && iter.next(e, row_lo, row_hi)) {
       for (int c = 0; c < p.kc; ++c) {
         if (!mbar_wait(raw_full(sr), phr, &s_abort)) { atomicExch(&g_tc_status, 16); ok = false; break; }
@@ -988,6 +1019,7 @@ tc_moe_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (++sr == RS) { sr = 0; phr ^= 1u; }
         if (++sb == BS) { sb = 0; phb ^= 1u; }
       }
+    }
     }
   }
 
