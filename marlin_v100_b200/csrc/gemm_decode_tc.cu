@@ -27,8 +27,9 @@
 // buffer which a small kernel adds in a fixed order (results repeat bit for bit).
 //
 // Warp roles (896 threads):  0 TMA producer | 1, 2 MMA issuers (one 128-column tile each; 1 owns the tensor
-// memory) | 3 digit sums | 4-7 and 24-27 epilogue (tile, 32-lane quadrant) | 8-23 dequant (quadrant = warp % 4,
-// 32-k block = (warp - 8) / 4).
+// memory) | 3 digit sums | 4-7 and 24-27 epilogue (tile, 32-lane quadrant) | 8-23 dequant (quadrant = warp % 4;
+// warps 8-15 take the even chunks of the CTA's sequence, 16-23 the odd ones; a warp converts two of the chunk's four
+// 32-k blocks).
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag, the kernel drains, frees
 // its tensor memory and reports through g_dtc_status.
 
@@ -259,10 +260,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     s_abort = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full(s), 1);
-      mbar_init(empty(s), DQ_WARPS + 1 + EPI_WARPS);
+      mbar_init(empty(s), DQ_WARPS / 2 + 1 + EPI_WARPS);
       mbar_init(mma_done(s), 2);
     }
-    for (int t = 0; t < TSTAGES; ++t) mbar_init(a_ready(t), DQ_WARPS);
+    for (int t = 0; t < TSTAGES; ++t) mbar_init(a_ready(t), DQ_WARPS / 2);
     for (int b = 0; b < 2; ++b) { mbar_init(d_free(b), EPI_WARPS); mbar_init(sum_full(b), 1); }
     mbar_init(drain_bar(0), 1);
     mbar_init(drain_bar(1), 1);
@@ -502,28 +503,33 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
   } else {
     // ---------------- dequant (warps 8-23) ----------------
-    const int quad = warp & 3, kb = (warp - 8) >> 2;
+    // Two groups of eight warps take alternate chunks (a warp converts two of the chunk's four 32-k blocks), so that
+    // one group's wait for its tensor-memory stores overlaps the other group's loads and byte transposes.
+    const int quad = warp & 3, kb0 = 2 * (((warp - 8) >> 2) & 1), grp = (warp - 8) >> 3;
     const int g = lane >> 2, t = lane & 3;
     const int nv = 2 * quad + (g >> 2), sub = g & 3;
-    // The thread's eight packed words of its 32-k block: k = 8t + (q ^ 2t), q = 0..7 (the rotation
+    // The thread's eight packed words of a 32-k block: k = 8t + (q ^ 2t), q = 0..7 (the rotation
     // spreads the 32 lanes over 32 banks); byte offsets inside the chunk, 128-byte swizzle folded in.
     int woff[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       const int kk = 8 * t + (q ^ (2 * t));       // k inside the 32-k block
       const int lk = kk & 15;
-      woff[q] = (kb * 2 + (kk >> 4)) * 2048 + lk * 128 + ((nv ^ (lk & 7)) << 4) + sub * 4;
+      woff[q] = (kb0 * 2 + (kk >> 4)) * 2048 + lk * 128 + ((nv ^ (lk & 7)) << 4) + sub * 4;
     }
     bool ok = true;
     int i = 0;
     for (; w.valid(); w.next(), ++i) {
+      if ((i & 1) != grp) continue;
       const int s = i & (STAGES - 1), ts = i & (TSTAGES - 1);
       if (ok && !mbar_wait(full(s), ((uint32_t)i / STAGES) & 1u, &s_abort)) { atomicExch(&g_dtc_status, 9); ok = false; }
-      uint32_t x[8];
+      uint32_t x[2][8];
       if (ok) {
         const uint32_t raw = base + s * STAGE_BYTES;
 #pragma unroll
-        for (int q = 0; q < 8; ++q) x[q] = lds32(raw + woff[q]);
+        for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+          for (int q = 0; q < 8; ++q) x[kk][q] = lds32(raw + woff[q] + kk * 4096);   // the next 32-k block is 4096 bytes on
       }
       // the operand stage is free once the MMAs of the chunk that used it last have completed
       if (ok && i >= TSTAGES) {
@@ -532,12 +538,15 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       }
       if (ok) {
         tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+        const int kb = kb0 + kk;
         // 4 x 4 byte transposes: o[c][b] = byte b of the four words of column c (four consecutive k slots)
         uint32_t o[2][4];
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          const uint32_t a01 = prmt(x[4 * c], x[4 * c + 1], 0x5140u), a23 = prmt(x[4 * c + 2], x[4 * c + 3], 0x5140u);
-          const uint32_t b01 = prmt(x[4 * c], x[4 * c + 1], 0x7362u), b23 = prmt(x[4 * c + 2], x[4 * c + 3], 0x7362u);
+          const uint32_t a01 = prmt(x[kk][4 * c], x[kk][4 * c + 1], 0x5140u), a23 = prmt(x[kk][4 * c + 2], x[kk][4 * c + 3], 0x5140u);
+          const uint32_t b01 = prmt(x[kk][4 * c], x[kk][4 * c + 1], 0x7362u), b23 = prmt(x[kk][4 * c + 2], x[kk][4 * c + 3], 0x7362u);
           o[c][0] = prmt(a01, a23, 0x5410u);
           o[c][1] = prmt(a01, a23, 0x7632u);
           o[c][2] = prmt(b01, b23, 0x5410u);
@@ -553,6 +562,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             tmem_st_16x256b(taddr, o[0][b] & 0x0f0f0f0fu, o[1][b] & 0x0f0f0f0fu,
                             (o[0][b] ^ 0x80808080u) & 0xf0f0f0f0u, (o[1][b] ^ 0x80808080u) & 0xf0f0f0f0u);
           }
+        }
         tmem_st_wait();
         tc_fence_before();
       }
