@@ -739,13 +739,17 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int r = 0; r < 2; ++r) {
       if (s_run_len[r] == 0) continue;
       const int g = s_run_g[r];
-      if (!mbar_wait_park(part_ready(r), 0, &s_abort, 2000)) { atomicExch(&g_si8_status, 10); break; }
-      if (!waited) { pdl_wait_prior_grid(); waited = true; }   // the counters were cleared by the kernel in front
+      // one thread waits for the epilogue warps (polling with short sleeps: a parked wait wakes up about half a
+      // microsecond late, and this wait is on the critical path of the CTA's last run); the other 127 block in the
+      // named barrier below, which costs no issue slots
       const int64_t ua = (int64_t)g * p.kc;
       const int64_t pa = unit_owner(ua, U, num_ctas), pb = unit_owner(ua + p.kc - 1, U, num_ctas);
       if (rt == 0) {
-        int last = 0;
-        if (s_abort == 0) {
+        int last = -1;
+        if (mbar_wait_sleep(part_ready(r), 0, &s_abort, 100)) last = 0;
+        else atomicExch(&g_si8_status, 10);
+        if (last == 0) pdl_wait_prior_grid();   // the counters were cleared by the kernel in front
+        if (last == 0 && s_abort == 0) {
           // One release-acquire atomic instead of fence, atomic, fence: the release is cumulative over the epilogue
           // warps' stores (ordered before this thread by part_ready), the acquire covers the other owners' stores
           // for every thread behind the barrier below.
@@ -758,7 +762,9 @@ stream_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       reduce_barrier();
       const int last = s_last;
       reduce_barrier();
+      if (last < 0) break;
       if (!last) continue;
+      if (!waited) { pdl_wait_prior_grid(); waited = true; }   // nothing is stored before the kernel in front is done
       constexpr int64_t SLOT = NTOK * kGroupN;
       // the first owner holds the group's first chunks (slot 1), every other one a run from midway (slot 0)
       const float4* first = reinterpret_cast<const float4*>(p.partials + (pa * 2 + 1) * SLOT);
