@@ -33,17 +33,18 @@
 // Warps (768 threads; 80 registers each, nothing spills): 0-7 epilogue (tile = warp / 4, 32-lane quadrant =
 // warp % 4) | 8-15 dequant (quadrant = warp % 4; warps 8-11 take the even chunks of the CTA's sequence, 12-15 the odd
 // ones, each warp both tiles and both 16-lane halves: one group's wait for its tensor-memory stores overlaps the
-// other group's loads and conversion) | 16 weight
-// producer | 17 and 19 MMA issuers (one 128-column tile each, on two different SM partitions: issuing is what
-// an MMA of this size costs; 17 owns the tensor memory) | 18 producer of the small per-chunk operands (digit
-// tile, digit sums, scale and zero rows) | 20-23 cross-CTA sums of the column groups shared with other CTAs.
+// other group's loads and conversion) | 16 weight producer | 17 and 19 MMA issuers on two different SM partitions
+// (issuing is what an MMA of this size costs; up to 16 rows each takes every other chunk with both 128-column tiles,
+// at 32 rows each takes one tile of every chunk; 17 owns the tensor memory) | 18 producer of the small per-chunk
+// operands (digit tile, digit sums, scale and zero rows) | 20-23 cross-CTA sums of the column groups shared with
+// other CTAs (one thread waits for the epilogue's partial sums, the others block in a named barrier).
 // Four operand stages and eight (up to 8 rows), four (up to 16) or two (up to 32) accumulator buffers in tensor memory: the
 // round trip MMA -> epilogue -> next MMA on the same buffer (about 1500 cycles) bounds the rate at one chunk per
 // round trip / buffers.
 // A stage's 16 KiB of packed weights are released as soon as the dequant warps have read them and refilled at
 // once, so all six stages (96 KiB per SM; eight stages measured 0.6 us slower per GEMM, eleven 1.5 us, bare copies
-// lose bandwidth beyond 128 KiB in flight per SM too) cover the DRAM latency; the small operands (7 KiB, served by L2) stay until the
-// chunk's MMAs and epilogue are done.
+// lose bandwidth beyond 128 KiB in flight per SM too) cover the DRAM latency; the small operands (7 KiB, served by
+// L2) stay until the chunk's MMAs and epilogue are done.
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag, the kernel drains, frees its tensor
 // memory and reports through g_si8_status.
 //
