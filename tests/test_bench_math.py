@@ -51,6 +51,10 @@ def test_records_of_the_default_line_and_their_data():
     # the streaming layout changes the dominant kernel of the decode sizes, and the traffic figure follows it
     assert b.dominant_kernel("dense_u4_g128_bf16_m16", 16, 8192, 28672, "streaming") == "stream_i8_kernel"
     assert b.dominant_kernel("dense_u8b128_ch_bf16_m16", 16, 8192, 28672, "streaming") == "stream_gemm_kernel"
+    # 17-32 rows stay on the integer kernel, 33-64 rows go to the 16-bit streaming kernel
+    assert b.dominant_kernel("dense_u4_g128_bf16_m32", 32, 8192, 28672, "streaming") == "stream_i8_kernel"
+    assert b.dominant_kernel("dense_u4_g128_bf16_m64", 64, 8192, 28672, "streaming") == "stream_gemm_kernel"
+    assert b.dominant_kernel("dense_u4_g128_bf16_m64", 64, 8192, 28672, "reference") == "tc_gemm_kernel"
     traffic = b.ncu_traffic("dense_u4_g128_bf16_m16", "stream_i8_kernel")
     assert traffic is not None and 1.0 <= traffic / b.algorithmic_bytes("u4", 8192, 28672, 128) <= 1.05
     assert b.ncu_traffic("dense_u4_g128_bf16_m16", "decode_tc_kernel") is None     # figure of another kernel
