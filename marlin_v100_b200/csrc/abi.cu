@@ -107,6 +107,19 @@ int dispatch(const GemmArgs& g) {
     if (gemm_stream_i8_accepts(g)) return launch_gemm_stream_i8(g);
     return g.act_dtype == MARLIN_B200_F16 ? launch_gemm_stream_f16(g) : launch_gemm_stream_bf16(g);
   }
+  // size_n % 256 != 0: the same kernels on a copy padded to the next multiple of 256 columns, when the scratch
+  // buffer holds it
+  if (gemm_pad_applies(g) && g.scratch != nullptr &&
+      g.scratch_bytes >= marlin_b200_gemm_scratch_bytes(g.size_m, g.size_n, g.size_k, g.format)) {
+    GemmArgs padded;
+    int rc = gemm_pad_prepare(g, &padded);
+    if (rc < 0) return rc;
+    if (rc == 0) {
+      rc = dispatch(padded);
+      if (rc != 0) return rc;
+      return gemm_pad_finish(g, padded);
+    }
+  }
   // M <= 16: weight-streaming kernel.  Larger M: tensor-memory kernel; shapes it does not take fall
   // back to passes of the streaming kernel, and anything else to the shape-agnostic kernel.
   if (g.size_m > 16) {
@@ -171,6 +184,13 @@ extern "C" int64_t marlin_b200_gemm_scratch_bytes(int64_t size_m, int64_t size_n
     const int f = format & ~MARLIN_B200_FMT_PREPARED;
     const int64_t b = (size_m <= 32 && (f == kU4B8 || f == kU4)) ? gemm_stream_i8_scratch_bytes(size_m, size_n, size_k) : 0;
     return a > b ? a : b;
+  }
+  if (size_n % 256 != 0 && size_n % 64 == 0 && size_k % 64 == 0 && size_m > 0) {
+    // the padded copy of the operands and of the output, then what the kernels need on N' columns
+    const int64_t n_pad = (size_n + 255) / 256 * 256;
+    const int64_t a = gemm_decode_scratch_bytes(size_m, n_pad, size_k, format);
+    const int64_t b = gemm_tc_scratch_bytes(size_m, n_pad, size_k);
+    return gemm_pad_scratch_bytes(size_m, size_n, size_k, format, a > b ? a : b);
   }
   const int64_t a = gemm_decode_scratch_bytes(size_m, size_n, size_k, format);
   const int64_t b = gemm_tc_scratch_bytes(size_m, size_n, size_k);

@@ -163,6 +163,11 @@ struct GemmArgs {
 
 // kernel launchers (one per translation unit)
 int launch_gemm_generic(const GemmArgs& g);
+// size_n % 256 != 0: operands copied into the 256-column form of a matrix padded to N' columns (gemm_pad.cu)
+bool gemm_pad_applies(const GemmArgs& g);
+int64_t gemm_pad_scratch_bytes(int64_t m, int64_t n, int64_t k, int format, int64_t inner);
+int gemm_pad_prepare(const GemmArgs& g, GemmArgs* padded);   // 1: the scratch buffer cannot hold it
+int gemm_pad_finish(const GemmArgs& g, const GemmArgs& padded);
 int launch_gemm_decode(const GemmArgs& g);          // returns 1 if the shape is not handled
 int64_t gemm_decode_scratch_bytes(int64_t m, int64_t n, int64_t k, int format);
 int launch_gemm_decode_tc(const GemmArgs& g);       // returns 1 if the shape is not handled

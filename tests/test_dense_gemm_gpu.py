@@ -250,3 +250,29 @@ def test_argument_errors(kw, match):
                         torch.empty(0, dtype=torch.int32, device="cuda"), qw.type_id,
                         kw.get("size_m", 2), kw.get("size_n", 64), 64, True, False, True,
                         bool(kw.get("zp_on_b8")))
+
+
+@pytest.mark.parametrize("fmt,dtype,m,k,n,gs", [
+    ("fp8", torch.bfloat16, 1, 5120, 3200, -1),      # a column shard of 25600 / 8
+    ("fp8", torch.bfloat16, 32, 5120, 3200, -1),
+    ("mxfp4", torch.bfloat16, 16, 1024, 3200, None),
+    ("nvfp4", torch.float16, 16, 512, 320, None),
+    ("u4", torch.bfloat16, 64, 1024, 832, 128),
+    ("u4b8", torch.float16, 300, 512, 1152, 128),
+    ("u8b128", torch.float16, 128, 512, 192, -1),
+])
+def test_n_not_a_multiple_of_256_takes_the_padded_path(fmt, dtype, m, k, n, gs):
+    """size_n % 256 != 0 with a scratch buffer of the advertised size: the operands are copied into the
+    256-column form of a matrix padded to the next multiple of 256 columns and the regular kernels run on it
+    (more than the one launch of the shape-agnostic kernel), with a bias crossing the boundary as well."""
+    from marlin_v100_b200 import _lib
+    lib = _lib.load()
+    a, qw = util.make_dense(m, k, n, fmt, dtype, group_size=gs, seed=21)
+    bias = (torch.randn(n, generator=torch.Generator().manual_seed(22)) * 0.5).to(dtype)
+    run_gemm(a, qw, bias=bias)   # warm-up: tensor maps, function attributes
+    before = lib.marlin_b200_launch_count()
+    out = run_gemm(a, qw, bias=bias)
+    launches = lib.marlin_b200_launch_count() - before
+    assert tuple(out.shape) == (m, n)
+    check(out, mo.dense_reference(a, qw.deq, bias))
+    assert launches >= 4, f"{launches} launches: the padded path did not run"
