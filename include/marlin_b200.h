@@ -134,6 +134,11 @@ int marlin_b200_restore_weights(const int32_t* prepared, int32_t* out, int64_t s
  *               [size_m][size_n], or two partial tiles per SM); a smaller buffer is accepted there and
  *               selects a cheaper cut or none (results stay within rounding of each other, and are
  *               bit-identical from run to run for one buffer size).
+ *               For size_n % 256 != 0 (size_n % 64 == 0, size_k % 64 == 0) the buffer also holds a copy of
+ *               the weights, scales, zero-points, bias and output padded to the next multiple of 256
+ *               columns, made on every call (the reference's packed layout differs for such widths and
+ *               the tensor-core kernels read the 256-column form); with a smaller buffer a slower
+ *               shape-agnostic kernel serves the call, same results within rounding.
  * With MARLIN_B200_FMT_PREPARED in `format`, b_q_weight is the streaming layout and one kernel family serves
  * every size_m (passes of up to 128 rows); scratch then holds one counter per 256-column group and two fp32
  * partial tiles per SM, and a buffer that is too small (or NULL) makes every CTA take whole column groups
